@@ -101,8 +101,69 @@ __global__ void qknorm_kv_write_kernel(float* __restrict__ q, long sq, const flo
   }
 }
 
+// Latent attention, one launch per step: warp per (token, vector).  Vector 0 is the token's cache row
+//   [ latent / rms(latent) * w  |  rotated shared key part ]   (rank + dr columns of the single key/value "head"),
+// vectors 1..H are the heads' rotated query parts, written behind the absorbed unrotated part of the same head in
+// qa (head h of token t at qa + t * sqa + h * sha, rank + dr columns).  Only the first `rdims` of the dr columns turn; (cos, sin) come from the angle p * freq[i] formed and
+// reduced to [-pi, pi] in double, times `mult`.  interleaved: pairs (2i, 2i + 1); else (i, i + rdims / 2).
+template <typename CT>
+__global__ void latent_kv_write_kernel(const float* __restrict__ q, long sq, int H, int dn, int dr, const float* __restrict__ dkv, long sd,
+                                       int rank, const float* __restrict__ w, float eps, const double* __restrict__ freq, int rdims,
+                                       float mult, int interleaved, const int* __restrict__ pos, const int* __restrict__ kv_slot,
+                                       CT* __restrict__ cache, int page, float* __restrict__ qa, long sqa, long sha,
+                                       __nv_bfloat16* __restrict__ qn, long T) {
+  const long wid = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= T * (H + 1)) return;
+  const long t = wid / (H + 1);
+  const int vec = static_cast<int>(wid - t * (H + 1));
+  const int D = rank + dr;
+  const double p = static_cast<double>(pos[t]);
+  const float* src = vec == 0 ? dkv + t * sd + rank : q + t * sq + static_cast<long>(vec - 1) * (dn + dr) + dn;
+  CT* crow = nullptr;
+  if (vec == 0) {
+    const int slot = kv_slot[t];
+    crow = cache + static_cast<long>(slot) * D;               // one head: cell = page index * page + offset = slot
+    const float* x = dkv + t * sd;
+    float ss = 0.f;
+    for (int c = lane; c < rank; c += 32) ss += x[c] * x[c];
+    ss = warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / static_cast<float>(rank) + eps);
+    for (int c = lane; c < rank; c += 32) st(crow, c, x[c] * r * w[c]);
+  }
+  float* qrow = vec == 0 ? nullptr : qa + t * sqa + static_cast<long>(vec - 1) * sha + rank;
+  if (vec > 0 && qn != nullptr) {                              // the head's unrotated columns as a bf16 GEMM operand [H, T, dn]
+    const float* qs = q + t * sq + static_cast<long>(vec - 1) * (dn + dr);
+    __nv_bfloat16* qd = qn + (static_cast<long>(vec - 1) * T + t) * dn;
+    for (int c = lane; c < dn; c += 32) qd[c] = __float2bfloat16_rn(qs[c]);
+  }
+  const int half = rdims / 2;
+  for (int i = lane; i < half; i += 32) {
+    double a = p * freq[i];
+    a -= 6.283185307179586476925 * rint(a * 0.15915494309189533577);
+    float sn, cs;
+    sincosf(static_cast<float>(a), &sn, &cs);
+    sn *= mult;
+    cs *= mult;
+    const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
+    const float u = src[iu], v = src[iv];
+    const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+    if (vec == 0) {
+      st(crow, rank + iu, ru);
+      st(crow, rank + iv, rv);
+    } else {
+      qrow[iu] = ru;
+      qrow[iv] = rv;
+    }
+  }
+  for (int c = rdims + lane; c < dr; c += 32) {                // columns past the rotated ones pass unchanged
+    if (vec == 0) st(crow, rank + c, src[c]);
+    else qrow[c] = src[c];
+  }
+}
+
 constexpr int kWarps = 4;
-constexpr int kMaxDvPerLane = 8;       // Dv <= 256
+constexpr int kMaxDvPerLane = 16;      // Dv <= 512
 
 // block per (token, query head); the window's keys are dealt to the warps in runs of 32 (one key per lane)
 template <typename CT, typename OT>
@@ -120,7 +181,7 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int p = pos[t];
   const int* bt = block_table + static_cast<long>(tok_entry[t]) * max_blocks;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) sq_[c] = q[t * sq + static_cast<long>(h) * D + c];
+  for (int c = threadIdx.x; c < D; c += blockDim.x) sq_[c] = q[t * sq + static_cast<long>(h) * (md.q_head_stride ? md.q_head_stride : D) + c];
   __syncthreads();
   const int lo = first_key(p, window, md.chunked);
   const int nkeys = p - lo + 1;
@@ -143,7 +204,7 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
       float d = 0.f;
       for (int c = 0; c < D; ++c) d += sq_[c] * ld(kr, c);
       sc = d * scale - slope * static_cast<float>(p - j);
-      vrow = cell * Dv;
+      vrow = cell * (md.kv_shared ? D : Dv);
     }
     const float mn = fmaxf(m, warp_max(sc));
     const float corr = expf(m - mn);               // m = -inf on the first run: exp(-inf) = 0
@@ -173,9 +234,9 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
     ml[2 * w + 1] = l;
   }
   __syncthreads();
-  float mt = -INFINITY;
+  float mt = md.head_sink != nullptr ? md.head_sink[h] : -INFINITY;       // the sink: a score with no key and no value
   for (int i = 0; i < kWarps; ++i) mt = fmaxf(mt, ml[2 * i]);
-  float lt = 0.f, f[kWarps];
+  float lt = md.head_sink != nullptr ? expf(md.head_sink[h] - mt) : 0.f, f[kWarps];
   for (int i = 0; i < kWarps; ++i) {
     f[i] = ml[2 * i] == -INFINITY ? 0.f : expf(ml[2 * i] - mt);
     lt += f[i] * ml[2 * i + 1];
@@ -219,7 +280,7 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float* o) {
   o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
 }
 
-template <typename CT, typename OT, int NQ>
+template <typename CT, typename OT, int NQ, int NVC>       // NVC: chunks of 128 value columns (Dv <= 128 NVC)
 __global__ void __launch_bounds__(kWarps * 32)
 window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __restrict__ k_cache, const CT* __restrict__ v_cache,
                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_entry,
@@ -253,19 +314,21 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
       float v = 0.f;
       if (qi < nqs) {
         const int hq = h0 + qi % hb;
-        v = q[static_cast<long>(t + qi / hb) * sq + static_cast<long>(hq) * D + c] * scale;
+        v = q[static_cast<long>(t + qi / hb) * sq + static_cast<long>(hq) * (md.q_head_stride ? md.q_head_stride : D) + c] * scale;
         if (md.head_scale != nullptr) v *= md.head_scale[hq];
       }
       qs[idx] = v;
     }
     __syncthreads();
-    float m[NQ], l[NQ], acc[NQ][4], slope[NQ];
+    float m[NQ], l[NQ], acc[NQ][4 * NVC], slope[NQ];
+    const long vstride = md.kv_shared ? D : Dv;
 #pragma unroll
     for (int i = 0; i < NQ; ++i) {
       slope[i] = (md.head_slope != nullptr && i < nqs) ? md.head_slope[h0 + i % hb] : 0.f;
       m[i] = -INFINITY;
       l[i] = 0.f;
-      acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll
+      for (int x = 0; x < 4 * NVC; ++x) acc[i][x] = 0.f;
     }
     for (int base = w * 32; base < nkeys; base += kWarps * 32) {
       const int j = lo + base + lane;
@@ -306,32 +369,39 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
           const float corr = expf(m[i] - mn);
           pr = valid ? expf(sc - mn) : 0.f;
           l[i] = l[i] * corr + warp_sum(pr);
-          acc[i][0] *= corr; acc[i][1] *= corr; acc[i][2] *= corr; acc[i][3] *= corr;
+#pragma unroll
+          for (int x = 0; x < 4 * NVC; ++x) acc[i][x] *= corr;
           m[i] = mn;
         }
         myp[lane * NQ + i] = pr;
       }
       __syncwarp();
       const int cnt = nkeys - base < 32 ? nkeys - base : 32;
-      const int c0 = lane * 4;
       for (int jj = 0; jj < cnt; ++jj) {
-        const long vr = __shfl_sync(0xffffffffu, cell, jj) * Dv;
-        float vv[4] = {0.f, 0.f, 0.f, 0.f};
-        if (c0 < Dv) load4(v_cache + vr + c0, vv);
+        const long vr = __shfl_sync(0xffffffffu, cell, jj) * vstride;
 #pragma unroll
-        for (int i = 0; i < NQ; ++i) {
-          const float pj = myp[jj * NQ + i];
-          acc[i][0] += pj * vv[0]; acc[i][1] += pj * vv[1]; acc[i][2] += pj * vv[2]; acc[i][3] += pj * vv[3];
+        for (int x = 0; x < NVC; ++x) {
+          const int c0 = lane * 4 + 128 * x;
+          float vv[4] = {0.f, 0.f, 0.f, 0.f};
+          if (c0 < Dv) load4(v_cache + vr + c0, vv);
+#pragma unroll
+          for (int i = 0; i < NQ; ++i) {
+            const float pj = myp[jj * NQ + i];
+            acc[i][4 * x] += pj * vv[0]; acc[i][4 * x + 1] += pj * vv[1]; acc[i][4 * x + 2] += pj * vv[2]; acc[i][4 * x + 3] += pj * vv[3];
+          }
         }
       }
       __syncwarp();
     }
-    const int c0 = lane * 4;
 #pragma unroll
     for (int i = 0; i < NQ; ++i) {
-      if (c0 < Dv) {
-        float* d = racc + (static_cast<long>(w) * NQ + i) * Dv + c0;
-        d[0] = acc[i][0]; d[1] = acc[i][1]; d[2] = acc[i][2]; d[3] = acc[i][3];
+#pragma unroll
+      for (int x = 0; x < NVC; ++x) {
+        const int c0 = lane * 4 + 128 * x;
+        if (c0 < Dv) {
+          float* d = racc + (static_cast<long>(w) * NQ + i) * Dv + c0;
+          d[0] = acc[i][4 * x]; d[1] = acc[i][4 * x + 1]; d[2] = acc[i][4 * x + 2]; d[3] = acc[i][4 * x + 3];
+        }
       }
       if (lane == 0) {
         rml[(w * NQ + i) * 2] = m[i];
@@ -341,9 +411,10 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
     __syncthreads();
     for (int idx = threadIdx.x; idx < nqs * Dv; idx += blockDim.x) {
       const int qi = idx / Dv, c = idx - qi * Dv;
-      float mt = -INFINITY;
+      const float sink = md.head_sink != nullptr ? md.head_sink[h0 + qi % hb] : -INFINITY;    // a score with no key and no value
+      float mt = sink;
       for (int x = 0; x < kWarps; ++x) mt = fmaxf(mt, rml[(x * NQ + qi) * 2]);
-      float lt = 0.f, a = 0.f;
+      float lt = md.head_sink != nullptr ? expf(sink - mt) : 0.f, a = 0.f;
       for (int x = 0; x < kWarps; ++x) {
         const float mx = rml[(x * NQ + qi) * 2];
         const float f = mx == -INFINITY ? 0.f : expf(mx - mt);
@@ -358,7 +429,7 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
   }
 }
 
-template <typename CT, typename OT, int NQ>
+template <typename CT, typename OT, int NQ, int NVC>
 cudaError_t launch_tile(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
                         const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T,
                         int Hq, int Hkv, int D, int Dv, int page, const NrlAttnMods& md, cudaStream_t s) {
@@ -366,7 +437,7 @@ cudaError_t launch_tile(const float* q, long sq, const void* k_cache, const void
   const int HB = per_g < NQ ? per_g : NQ, QT = NQ / HB > 1 ? NQ / HB : 1;
   const size_t smem = sizeof(float) * (static_cast<size_t>(NQ) * D + kWarps * 32 * NQ + static_cast<size_t>(kWarps) * NQ * Dv + kWarps * NQ * 2);
   if (smem > 160 * 1024) return cudaErrorInvalidValue;
-  auto kern = window_attention_tile_kernel<CT, OT, NQ>;
+  auto kern = window_attention_tile_kernel<CT, OT, NQ, NVC>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -383,12 +454,21 @@ template <typename CT, typename OT>
 cudaError_t launch_tile_nq(int nq, const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                            int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out,
                            long so, int T, int Hq, int Hkv, int D, int Dv, int page, const NrlAttnMods& md, cudaStream_t s) {
-#define NRL_WA(NQ_) return launch_tile<CT, OT, NQ_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, \
-                                                     out_scale, out, so, T, Hq, Hkv, D, Dv, page, md, s)
-  if (nq <= 2) NRL_WA(2);
-  if (nq <= 4) NRL_WA(4);
-  if (nq <= 8) NRL_WA(8);
-  NRL_WA(16);
+#define NRL_WA(NQ_, NVC_) return launch_tile<CT, OT, NQ_, NVC_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, \
+                                                                 scale, out_scale, out, so, T, Hq, Hkv, D, Dv, page, md, s)
+  if (Dv > 256) {                        // wider values: fewer queries per block, so that the sums still fit the registers
+    if (nq <= 2) NRL_WA(2, 4);
+    NRL_WA(4, 4);
+  }
+  if (Dv > 128) {
+    if (nq <= 2) NRL_WA(2, 2);
+    if (nq <= 4) NRL_WA(4, 2);
+    NRL_WA(8, 2);
+  }
+  if (nq <= 2) NRL_WA(2, 1);
+  if (nq <= 4) NRL_WA(4, 1);
+  if (nq <= 8) NRL_WA(8, 1);
+  NRL_WA(16, 1);
 #undef NRL_WA
 }
 
@@ -428,16 +508,40 @@ cudaError_t nrl_kv_write_blend(const float* k, long sk, float* v, long sv, const
   return cudaGetLastError();
 }
 
+cudaError_t nrl_latent_kv_write(const float* q, long sq, int H, int dn, int dr, const float* dkv, long sd, int rank, const float* w,
+                                float eps, const double* freq, int rdims, float mult, int interleaved, const int* pos, const int* kv_slot,
+                                void* cache, int cache_f32, int page, float* qa, long sqa, long sha, void* qn, int T, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (rdims < 0 || rdims > dr || rdims % 2 != 0 || rank < 1 || H < 1) return cudaErrorInvalidValue;
+  const long warps = static_cast<long>(T) * (H + 1);
+  const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
+  if (cache_f32)
+    latent_kv_write_kernel<float><<<blocks, 128, 0, s>>>(q, sq, H, dn, dr, dkv, sd, rank, w, eps, freq, rdims, mult, interleaved, pos,
+                                                         kv_slot, static_cast<float*>(cache), page, qa, sqa, sha, static_cast<__nv_bfloat16*>(qn), T);
+  else
+    latent_kv_write_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(q, sq, H, dn, dr, dkv, sd, rank, w, eps, freq, rdims, mult, interleaved,
+                                                                 pos, kv_slot, static_cast<__nv_bfloat16*>(cache), page, qa, sqa, sha,
+                                                                 static_cast<__nv_bfloat16*>(qn), T);
+  return cudaGetLastError();
+}
+
 cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, const void* v_cache, int cache_f32,
                                  const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
                                  float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D, int Dv,
                                  int page, int single_token, int impl, int nsplit, float* part, const NrlAttnMods* mods, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
-  if (Dv > 32 * kMaxDvPerLane || Hq % Hkv != 0 || window < 1 || cache_f32 != out_f32) return cudaErrorInvalidValue;
+  if (Hq % Hkv != 0 || window < 1 || cache_f32 != out_f32) return cudaErrorInvalidValue;
   NrlAttnMods md = {0, nullptr, nullptr, nullptr, 0};
   if (mods != nullptr) md = *mods;
+  if (md.kv_shared && (Dv > D || v_cache != k_cache)) return cudaErrorInvalidValue;
+  // latent attention (one shared row per token is key and value of every head, causal) over bf16 pages: its own tensor-core kernels
+  if ((impl == 0 || impl == 3) && !cache_f32 && md.kv_shared && Hkv == 1 && window >= (1 << 30) && !md.chunked &&
+      md.head_scale == nullptr && md.head_slope == nullptr && nrl_latent_attention_mma_fits(out, so, D, Dv, page))
+    return nrl_latent_attention_mma(q, sq, k_cache, block_table, max_blocks, tok_entry, pos, scale, out_scale, out, so, T, Hq, D, Dv, page,
+                                    single_token, nsplit, part, &md, s);
   // prompt portions over bf16 pages: tensor cores
-  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page)) {
+  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) &&
+      md.head_sink == nullptr && !md.kv_shared) {
     if (single_token && nsplit >= 1 && part != nullptr)
       return nrl_window_attention_decode(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out,
                                          so, T, Hq, Hkv, D, Dv, page, nsplit, part, &md, s);
@@ -445,7 +549,7 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
                                     T, Hq, Hkv, D, Dv, page, single_token, &md, s);
   }
   if (impl == 3) return cudaErrorInvalidValue;
-  if (impl != 2 && Dv <= 128 && Dv % 4 == 0 && D <= 512) {
+  if (impl != 2 && Dv <= 512 && Dv % 4 == 0 && D <= 1024 && (!md.kv_shared || D % 4 == 0)) {
     // queries per block: the heads of one key/value head for single-token steps, 16 (tokens x heads) when entries hold runs
     const int nq = single_token ? Hq / Hkv : 16;
     return cache_f32 ? launch_tile_nq<float, float>(nq, q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale,
@@ -454,7 +558,7 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
                                                                     window, scale, out_scale, out, so, T, Hq, Hkv, D, Dv, page, md, s);
   }
   const size_t smem = sizeof(float) * (D + kWarps * Dv + 2 * kWarps);
-  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024 || Dv > 32 * kMaxDvPerLane) return cudaErrorInvalidValue;
   const dim3 grid(T, Hq);
   if (cache_f32)
     window_attention_kernel<float, float><<<grid, kWarps * 32, smem, s>>>(

@@ -19,6 +19,11 @@ typedef struct {
   const float* head_slope;   // [Hq] or null: head_slope[h] * (p - j) is taken off the score
   const float* gate;         // [T, Hq] float (row stride gate_stride) or null: head h's output is multiplied by sigmoid(gate[t, h])
   long gate_stride;
+  const float* head_sink;    // [Hq] or null: the softmax denominator also holds exp(head_sink[h]), a score without key or value
+                             // (it is not multiplied by the scale and counts once)
+  int kv_shared;             // 1: values are the first Dv columns of the key rows (v_cache == k_cache, rows of D): latent attention
+  long q_head_stride;        // 0: head h of token t starts at q[t * sq + h * D]; else at q[t * sq + h * q_head_stride] (queries stored
+                             // head-major, as a batched GEMM leaves them); scalar and latent kernels only
 } NrlAttnMods;
 
 extern "C" {
@@ -55,12 +60,36 @@ cudaError_t nrl_moe_route(const float* router, long sr, const float* router_bias
 //   nrl_gather_rows16: out[r] = in[row_token[r]] for rows of W 16-bit elements.
 //   nrl_swiglu_rows: act[r, c] (bf16) = silu(gu[r, c]) * gu[r, ff + c].
 //   nrl_moe_combine: out[t] (float) = sum_k wts[t, k] * y[slot_of[t * top + k]] in the order of k.
-cudaError_t nrl_moe_plan(const int* ids, int R, int top, int E, int tile_rows, int* slot_of, int* row_token, int* seg, int* tiles,
+// n_real <= E: experts n_real .. E-1 get rows but no tiles (identity experts); nrl_moe_combine skips pairs of weight 0.
+cudaError_t nrl_moe_plan(const int* ids, int R, int top, int E, int n_real, int tile_rows, int* slot_of, int* row_token, int* seg, int* tiles,
                          int* num_tiles, cudaStream_t s);
 cudaError_t nrl_gather_rows16(const void* in, long in_stride, const int* row_token, void* out, int R, int W, cudaStream_t s);
 cudaError_t nrl_swiglu_rows(const float* gu, long sg, void* act, long sa, int R, int ff, cudaStream_t s);
 cudaError_t nrl_moe_combine(const float* y, long sy, const int* slot_of, const float* wts, int top, float* out, long so, int T, int W,
                             cudaStream_t s);
+
+// Stream with the norm on the sublayer's output only (sublayers read x itself).
+//   nrl_embed_norm:          x[t] = e / sqrt(mean(e^2) + eps) * w, e = embed[tok[t]] (typed table);  h = x (typed)
+//   nrl_post_norm_residual:  y = o + self_w[t] * x (self_w [T] or null: y = o);  x += y / sqrt(mean(y^2) + eps) * w_post;
+//                            h (typed, may be null) = w_pre ? x / sqrt(mean(x^2) + eps) * w_pre : x
+cudaError_t nrl_embed_norm(const void* embed, int w_f32, const int* tok, const float* w, float eps, float* x, void* h, int h_f32, int T,
+                           int W, cudaStream_t s);
+cudaError_t nrl_post_norm_residual(float* x, const float* o, const float* self_w, const float* w_post, const float* w_pre, float eps,
+                                   void* h, int h_f32, int T, int W, cudaStream_t s);
+// Gated token-side input: out[t, c] (typed, row stride so) = gelu_tanh(u[t, c]) * table[tok[t], col0 + c] for c < C, 0 for C <= c < Cpad
+// (u float, row stride su; table typed, row stride st_).
+cudaError_t nrl_side_gate(const float* u, long su, const void* table, long st_, int w_f32, int col0, const int* tok, void* out, long so,
+                          int out_f32, int T, int C, int Cpad, cudaStream_t s);
+// out[t, c] (typed) = silu(in[t, c]) * in[t, C + c] * (rgate ? sigmoid(rgate[t * srg]) : 1)
+cudaError_t nrl_swiglu_cols(const float* in, long si, const float* rgate, long srg, void* out, long so, int out_f32, int T, int C,
+                            cudaStream_t s);
+// Routing by a softmax over all E router outputs; the last E - n_real are identity experts.  The `top` largest
+// softmax + correction (correction [E] or null; ties: lowest index) are chosen; weight = softmax / (sum over the chosen + 1e-20)
+// * route_scale.  ids [T, top]; wts [T, top] (0 for a chosen identity expert); self_w [T] = summed weights of the chosen
+// identity experts (needed when n_real < E).  Dense form as nrl_moe_route, over the n_real experts.
+cudaError_t nrl_moe_route_all(const float* router, long sr, const float* correction, int E, int n_real, int top, float route_scale,
+                              const float* gu, long sgu, int ff, void* act, long sa, int act_f32, int* ids, float* wts, float* self_w,
+                              int T, cudaStream_t s);
 
 // Layer boundary of a depth-weighted residual stream.  results: float [n_results_cap, stride_r] with rows of W.
 //   if (o)  results[i] = xprev + o                      (closes the previous layer)
@@ -106,7 +135,13 @@ cudaError_t nrl_delta_prep(float* qkv, long sq, int col_k, const float* b_raw, l
                            const float* dt_bias, const float* A_log, float* beta, float* decay, int T, int heads, int kv_heads,
                            int D, int per_channel, cudaStream_t s);
 
+// Gated linear attention inputs.  qkv float [T, *] (row stride sq): q at column 0 (heads*D) is multiplied by D^-1/2 in place.
+// decay [T, heads*D] = sigmoid(a_raw + a_bias)^(1 / tau) per key channel (a_raw float, row stride sa; a_bias [heads*D] or null).
+cudaError_t nrl_gla_prep(float* qkv, long sq, const float* a_raw, long sa, const float* a_bias, float tau, float* decay, int T,
+                         int heads, int D, cudaStream_t s);
+
 // Gated delta rule scan.  Per head: S = g S (rows);  u = beta (v - S^T k);  S += k u^T;  o = S^T q.
+// beta == nullptr: plain accumulation, u = v (gated linear attention: S = diag(g) S + k v^T).
 // state float [slots, heads, D, Dv];  o float [T, heads*Dv].
 cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, const float* beta, const float* decay, float* state,
                            float* o, const int* cu, const int* start, const int* state_slot, int E, int heads, int kv_heads, int D,
@@ -118,6 +153,17 @@ cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, cons
 cudaError_t nrl_qknorm_kv_write(float* q, long sq, const float* k, long sk, const float* v, long sv, const float* qw, const float* kw,
                                 float eps, void* k_cache, void* v_cache, int cache_f32, const int* kv_slot, int T, int Hq, int Hkv,
                                 int D, int Dv, int page, cudaStream_t s);
+
+// Latent attention, write side.  dkv float [T, rank + dr] (row stride sd): the first `rank` columns are RMS-normed with weight w
+// [rank] (eps inside the root), the last dr are one key part shared by all heads; both go into the token's row of `cache`
+// (typed [pages, 1, page, rank + dr]).  q float [T, H * (dn + dr)]: every head's last dr columns go to qa [T, H, rank + dr]
+// (row stride sqa, head stride sha) behind the head's `rank` absorbed columns, which the caller fills; qn (bf16 [H, T, dn]) or
+// null: the heads' first dn columns as the operand of that batched GEMM.  The first `rdims` of the dr columns
+// of keys and queries are rotated by the angles pos * freq[i] (freq double [rdims / 2]), cos and sin times `mult`;
+// interleaved = 1 pairs column 2i with 2i + 1, 0 pairs i with i + rdims / 2.
+cudaError_t nrl_latent_kv_write(const float* q, long sq, int H, int dn, int dr, const float* dkv, long sd, int rank, const float* w,
+                                float eps, const double* freq, int rdims, float mult, int interleaved, const int* pos, const int* kv_slot,
+                                void* cache, int cache_f32, int page, float* qa, long sqa, long sha, void* qn, int T, cudaStream_t s);
 
 // Keys and values of a step's tokens into their pages, the values optionally blended with another layer's values of the
 // same tokens:  v <- (1 - lambda[0]) v + lambda[0] v_other  (v_other float, row stride svo, null: plain copy; lambda on device).
@@ -138,6 +184,17 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
 // blocks per (token, key/value head) walks its own pages and a second launch merges the parts; nrl_window_attention_splits
 // proposes the count (0: the shape does not fit).
 // `impl`: 0 picks by shape and step kind, 1 the scalar tile kernel, 2 one block per (token, head), 3 the tensor-core kernel.
+
+// Latent attention on the tensor cores (attention_latent_mma.cu): causal attention of H absorbed queries per token (q float
+// [T, H * D]) over bf16 pages [pages, 1, 16, D] whose rows are key and, in their first Dv columns, value of every head; sink
+// and gate from `mods`.  `_fits`: D, Dv multiples of 8, Dv <= D <= 576.  Single-token steps with nsplit >= 1 and `part` float
+// [T, H, 4 nsplit, Dv + 2] use the per-warp page walk + merge; `_splits` proposes the count.
+int nrl_latent_attention_mma_fits(const void* out, long so, int D, int Dv, int page);
+int nrl_latent_attention_splits(int T, int H, int Dv, int max_blocks);
+cudaError_t nrl_latent_attention_mma(const float* q, long sq, const void* cache, const int* block_table, int max_blocks,
+                                     const int* tok_entry, const int* pos, float scale, float out_scale, void* out, long so, int T, int H,
+                                     int D, int Dv, int page, int single_token, int nsplit, float* part, const NrlAttnMods* mods,
+                                     cudaStream_t s);
 
 // Tensor-core kernel for prompt portions over bf16 pages of 16 tokens (attention_window_mma.cu); `_fits` says whether the
 // shapes and the output's alignment allow it.

@@ -13,7 +13,7 @@ namespace {
 // One block.  ids [R] (R = tokens * top): expert of every pair.  Outputs: slot_of[R] (row of the pair in expert order),
 // row_token[R] (token of every row), seg[E + 1] (first row of every expert), tiles [*, 3] = (expert, first row, end row of the
 // expert) for every `tile_rows` rows of every expert that has rows, num_tiles[1].
-__global__ void moe_plan_kernel(const int* __restrict__ ids, int R, int top, int E, int tile_rows, int* __restrict__ slot_of,
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int R, int top, int E, int n_real, int tile_rows, int* __restrict__ slot_of,
                                 int* __restrict__ row_token, int* __restrict__ seg, int* __restrict__ tiles, int* __restrict__ num_tiles) {
   extern __shared__ int sh[];
   int* cnt = sh;             // [E]
@@ -27,7 +27,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int R, int top, int
     for (int e = 0; e < E; ++e) {
       start[e] = run;
       const int end = run + cnt[e];
-      for (int m0 = run; m0 < end; m0 += tile_rows) {
+      for (int m0 = run; m0 < end && e < n_real; m0 += tile_rows) {       // identity experts (e >= n_real) have no GEMM tiles
         tiles[3 * nt] = e;
         tiles[3 * nt + 1] = m0;
         tiles[3 * nt + 2] = end;
@@ -90,6 +90,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, long sy, const i
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < top; ++k) {
       const float w = wts[t * top + k];
+      if (w == 0.f) continue;                       // an identity expert's pair: its row was never computed
       const float4 v = *reinterpret_cast<const float4*>(y + static_cast<long>(slot_of[t * top + k]) * sy + c);
       acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
     }
@@ -106,11 +107,11 @@ inline int grid_for(long n, int threads) {
 
 extern "C" {
 
-cudaError_t nrl_moe_plan(const int* ids, int R, int top, int E, int tile_rows, int* slot_of, int* row_token, int* seg, int* tiles,
+cudaError_t nrl_moe_plan(const int* ids, int R, int top, int E, int n_real, int tile_rows, int* slot_of, int* row_token, int* seg, int* tiles,
                          int* num_tiles, cudaStream_t s) {
   if (R <= 0) return cudaSuccess;
-  if (E < 1 || E > 8192 || top < 1 || tile_rows < 1) return cudaErrorInvalidValue;
-  moe_plan_kernel<<<1, 1024, sizeof(int) * (2 * E + 1), s>>>(ids, R, top, E, tile_rows, slot_of, row_token, seg, tiles, num_tiles);
+  if (E < 1 || E > 8192 || top < 1 || tile_rows < 1 || n_real < 0 || n_real > E) return cudaErrorInvalidValue;
+  moe_plan_kernel<<<1, 1024, sizeof(int) * (2 * E + 1), s>>>(ids, R, top, E, n_real, tile_rows, slot_of, row_token, seg, tiles, num_tiles);
   return cudaGetLastError();
 }
 

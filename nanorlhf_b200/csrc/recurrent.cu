@@ -213,6 +213,19 @@ __global__ void delta_prep_kernel(float* __restrict__ qkv, long sq, int col_k, c
   }
 }
 
+// Gated linear attention inputs, block per token: q (columns 0 .. heads*D-1 of qkv, in place) times D^-1/2, and the decay of every
+// key channel  decay[t, i] = sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau)  with z = a_raw[t, i] + a_bias[i].
+__global__ void gla_prep_kernel(float* __restrict__ qkv, long sq, const float* __restrict__ a_raw, long sa, const float* __restrict__ a_bias,
+                                float inv_tau, float* __restrict__ decay, int n, int D) {
+  const long t = blockIdx.x;
+  const float qscale = 1.f / sqrtf(static_cast<float>(D));
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    qkv[t * sq + i] *= qscale;
+    const float z = a_raw[t * sa + i] + (a_bias != nullptr ? a_bias[i] : 0.f);
+    decay[t * n + i] = expf(-softplus(-z) * inv_tau);
+  }
+}
+
 // block per (entry, head); thread (r, v) owns column v of S [D, Dv] for rows d = r, r + R, ...
 // One pass over S forms the decayed state, S^T k and S^T q; the read-out of the written state is o = S^T q + u (k . q).
 __global__ void delta_scan_kernel(const float* __restrict__ qkv, long sq, int col_k, int col_v, const float* __restrict__ beta,
@@ -267,7 +280,8 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, long sq, int co
         sk += red[q * Dv + v];
         sq_ += red[(R + q) * Dv + v];
       }
-      const float u = beta[static_cast<long>(t) * heads + h] * (row[col_v + h * Dv + v] - sk);
+      const float vt = row[col_v + h * Dv + v];
+      const float u = beta != nullptr ? beta[static_cast<long>(t) * heads + h] * (vt - sk) : vt;   // no beta: plain accumulation
       if (r == 0) o[static_cast<long>(t) * heads * Dv + h * Dv + v] = sq_ + u * kq[0];
       for (int d = r; d < D; d += R) S[d * Dv + v] += vk[d] * u;
     }
@@ -405,7 +419,7 @@ delta_scan_reg_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
     pre[i] = idx < L ? *src(t0, idx) : 0.f;
   }
   if (live) pre_v = qkv[static_cast<long>(t0) * sq + col_v + h * Dv + c];
-  pre_beta = beta[static_cast<long>(t0) * heads + h];
+  pre_beta = beta != nullptr ? beta[static_cast<long>(t0) * heads + h] : 0.f;
   for (int t = t0; t < t1; ++t) {
     float* v = vec + ((t - t0) & 1) * L;
 #pragma unroll
@@ -422,7 +436,7 @@ delta_scan_reg_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
         if (idx < L) pre[i] = *src(t + 1, idx);
       }
       if (live) pre_v = qkv[static_cast<long>(t + 1) * sq + col_v + h * Dv + c];
-      pre_beta = beta[static_cast<long>(t + 1) * heads + h];
+      pre_beta = beta != nullptr ? beta[static_cast<long>(t + 1) * heads + h] : 0.f;
     }
     const float* vq = v;
     const float* vk = v + D;
@@ -452,7 +466,7 @@ delta_scan_reg_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
         sq_ += red[(R + x) * Dv + c];
         kq += rkq[x];
       }
-      const float u = b_cur * (v_cur - sk);
+      const float u = beta != nullptr ? b_cur * (v_cur - sk) : v_cur;
       if (r == 0) o[static_cast<long>(t) * heads * Dv + h * Dv + c] = sq_ + u * kq;
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
@@ -604,7 +618,7 @@ delta_scan_col_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
       }
     }
     pre_v = live ? row[col_v + h * Dv + c] : 0.f;
-    pre_beta = beta[static_cast<long>(t) * heads + h];
+    pre_beta = beta != nullptr ? beta[static_cast<long>(t) * heads + h] : 0.f;
   };
   if (t0 < t1) fetch(t0);
   for (int t = t0; t < t1; ++t) {
@@ -635,7 +649,7 @@ delta_scan_col_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
     }
     float sk = (pk[0] + pk[1]) + (pk[2] + pk[3]);
     if (SPLIT == 2) sk += __shfl_xor_sync(0xffffffffu, sk, 1);
-    const float u = b_cur * (v_cur - sk);
+    const float u = beta != nullptr ? b_cur * (v_cur - sk) : v_cur;
     float po[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < RH / 4; ++i) {                         // S <- S + k u^T;  o = S^T q sees this token's write
@@ -795,6 +809,14 @@ cudaError_t nrl_delta_prep(float* qkv, long sq, int col_k, const float* b_raw, l
   if (T <= 0) return cudaSuccess;
   delta_prep_kernel<<<T, 128, 0, s>>>(qkv, sq, col_k, b_raw, sb, a_raw, sa, dt_bias, A_log, beta, decay, heads, kv_heads, D,
                                       per_channel);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_gla_prep(float* qkv, long sq, const float* a_raw, long sa, const float* a_bias, float tau, float* decay, int T,
+                         int heads, int D, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (!(tau > 0.f)) return cudaErrorInvalidValue;
+  gla_prep_kernel<<<T, 128, 0, s>>>(qkv, sq, a_raw, sa, a_bias, 1.f / tau, decay, heads * D, D);
   return cudaGetLastError();
 }
 

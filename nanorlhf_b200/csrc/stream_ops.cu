@@ -335,6 +335,222 @@ __global__ void moe_route_kernel(const float* __restrict__ router, long sr, cons
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Stream with the norm on the sublayer's OUTPUT only: sublayers read x itself, x += rms_norm(sublayer(x)) * w.
+// ---------------------------------------------------------------------------------------------------------------------
+// x[t] = e / sqrt(mean(e^2) + eps) * w with e = embed[tok[t]];  h = x (typed).  One block per token.
+template <typename WT, typename HT>
+__global__ void embed_norm_kernel(const WT* __restrict__ embed, const int* __restrict__ tok, const float* __restrict__ w, float eps,
+                                  float* __restrict__ x, HT* __restrict__ h, int W) {
+  __shared__ float red[32];
+  const long t = blockIdx.x, a = static_cast<long>(tok[t]) * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = ld(embed, a + c);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / static_cast<float>(W) + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = ld(embed, a + c) * r * w[c];
+    x[t * W + c] = v;
+    st(h, t * W + c, v);
+  }
+}
+
+// Sublayer boundary, one block per token, the row staged in shared memory (o and x are read once, x and h written once):
+//   y = o + self_w[t] * x   (self_w == nullptr: y = o);   x += y / sqrt(mean(y^2) + eps) * w_post
+//   h = w_pre ? x / sqrt(mean(x^2) + eps) * w_pre : x                                 (typed)
+template <typename HT, int V>
+__global__ void post_norm_residual_kernel(float* __restrict__ x, const float* __restrict__ o, const float* __restrict__ self_w,
+                                          const float* __restrict__ w_post, const float* __restrict__ w_pre, float eps,
+                                          HT* __restrict__ h, int W) {
+  extern __shared__ __align__(16) float rowbuf[];       // [W]: y, then the new x
+  __shared__ float red[32];
+  const long row = static_cast<long>(blockIdx.x) * W;
+  const float sw = self_w != nullptr ? self_w[blockIdx.x] : 0.f;
+  const float inv = 1.f / static_cast<float>(W);
+  float ss = 0.f;
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    float y[V], xv[V];
+    ldv<V>(o + row + c, y);
+    if (self_w != nullptr) {
+      ldv<V>(x + row + c, xv);
+#pragma unroll
+      for (int e = 0; e < V; ++e) y[e] += sw * xv[e];
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      ss += y[e] * y[e];
+      rowbuf[c + e] = y[e];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss * inv + eps);
+  float s2 = 0.f;
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {       // a thread re-reads the columns it staged itself
+    float xv[V], wv[V];
+    ldv<V>(x + row + c, xv);
+    ldv<V>(w_post + c, wv);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      xv[e] += rowbuf[c + e] * r * wv[e];
+      rowbuf[c + e] = xv[e];
+      s2 += xv[e] * xv[e];
+    }
+    stv<V>(x + row + c, xv);
+    if (h != nullptr && w_pre == nullptr) stv<V>(h + row + c, xv);
+  }
+  if (h == nullptr || w_pre == nullptr) return;
+  s2 = block_sum(s2, red);
+  const float r2 = 1.f / sqrtf(s2 * inv + eps);
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    float hv[V], wv[V];
+    ldv<V>(w_pre + c, wv);
+#pragma unroll
+    for (int e = 0; e < V; ++e) hv[e] = rowbuf[c + e] * r2 * wv[e];
+    stv<V>(h + row + c, hv);
+  }
+}
+
+__device__ __forceinline__ float gelu_tanh_(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// Gated token-side input: out[t, c] (typed, row stride so; columns C..Cpad-1 zero) = gelu_tanh(u[t, c]) * table[tok[t], col0 + c]
+template <typename WT, typename OT>
+__global__ void side_gate_kernel(const float* __restrict__ u, long su, const WT* __restrict__ table, long st_, int col0,
+                                 const int* __restrict__ tok, OT* __restrict__ out, long so, long T, int C, int Cpad) {
+  const long n = T * Cpad;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < n; idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long t = idx / Cpad;
+    const int c = static_cast<int>(idx - t * Cpad);
+    float v = 0.f;
+    if (c < C) v = gelu_tanh_(u[t * su + c]) * ld(table, static_cast<long>(tok[t]) * st_ + col0 + c);
+    st(out, t * so + c, v);
+  }
+}
+
+// out[t, c] (typed) = silu(in[t, c]) * in[t, C + c] * (rgate ? sigmoid(rgate[t * srg]) : 1):  SwiGLU over [gate | up] columns with an
+// optional sigmoid gate per row
+template <typename OT>
+__global__ void swiglu_cols_kernel(const float* __restrict__ in, long si, const float* __restrict__ rgate, long srg, OT* __restrict__ out,
+                                   long so, long T, int C) {
+  const long n = T * C;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < n; idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long t = idx / C;
+    const int c = static_cast<int>(idx - t * C);
+    const float g = in[t * si + c], up = in[t * si + C + c];
+    float v = g * sigmoidf_(g) * up;
+    if (rgate != nullptr) v *= sigmoidf_(rgate[t * srg]);
+    st(out, t * so + c, v);
+  }
+}
+
+// the same, four columns per thread (128-bit loads, 64- / 128-bit stores)
+template <typename OT>
+__global__ void swiglu_cols_vec4_kernel(const float* __restrict__ in, long si, const float* __restrict__ rgate, long srg,
+                                        OT* __restrict__ out, long so, long T, int C4) {
+  const long n = T * C4;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < n; idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long t = idx / C4;
+    const int c = static_cast<int>(idx - t * C4) * 4;
+    float g[4], up[4], v[4];
+    ldv<4>(in + t * si + c, g);
+    ldv<4>(in + t * si + 4 * C4 + c, up);
+    const float rg = rgate != nullptr ? sigmoidf_(rgate[t * srg]) : 1.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = g[i] * sigmoidf_(g[i]) * up[i] * rg;
+    st4(out + t * so + c, v);
+  }
+}
+
+// Routing by a softmax over ALL router outputs, one warp per token.  E outputs, of which the last E - n_real are identity
+// experts (their result is the expert's input).  s = softmax(z);  the `top` largest s + correction are chosen (ties: lowest
+// index);  weight = s / (sum of the chosen s + 1e-20) * route_scale.
+//   ids [T, top] int;  wts [T, top] float: the weight, 0 for a chosen identity expert;  self_w [T]: the identity experts' weights, summed
+//   act != nullptr (dense form):  act[t, e*ff + c] = weight_e * silu(gu[t, e*2ff + c]) * gu[t, e*2ff + ff + c] for e < n_real, 0 if not chosen
+template <typename OT>
+__global__ void moe_route_all_kernel(const float* __restrict__ router, long sr, const float* __restrict__ correction, int E, int n_real,
+                                     int top, float route_scale, const float* __restrict__ gu, long sgu, int ff, OT* __restrict__ act,
+                                     long sa, int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ self_w) {
+  extern __shared__ float smf[];
+  float* sc = smf;                // [E] softmax scores
+  float* ch = sc + E;             // [E] choice scores, -inf once taken
+  float* wsel = ch + E;           // [E] weight, 0 = not chosen
+  __shared__ int chosen[64];
+  const long t = blockIdx.x;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, router[t * sr + e]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(router[t * sr + e] - mx);
+      sc[e] = p;
+      den += p;
+    }
+    den = warp_sum(den);
+    for (int e = lane; e < E; e += 32) {
+      const float p = sc[e] / den;
+      sc[e] = p;
+      ch[e] = p + (correction != nullptr ? correction[e] : 0.f);
+      wsel[e] = 0.f;
+    }
+    __syncwarp();
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      float best = -INFINITY;
+      int bi = E;
+      for (int e = lane; e < E; e += 32) {
+        const float v = ch[e];
+        if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      sum += sc[bi];
+      __syncwarp();
+      if (lane == 0) {
+        ch[bi] = -INFINITY;
+        chosen[k] = bi;
+      }
+      __syncwarp();
+    }
+    const float norm = route_scale / (sum + 1e-20f);
+    float idw = 0.f;
+    for (int k = 0; k < top; ++k) {                         // every lane walks the chosen in order: same sums on all lanes
+      const int e = chosen[k];
+      const float w = sc[e] * norm;
+      if (e >= n_real) idw += w;
+      if (lane == 0) {
+        if (e < n_real) wsel[e] = w;
+        if (ids != nullptr) ids[t * top + k] = e;
+        if (wts != nullptr) wts[t * top + k] = e < n_real ? w : 0.f;
+      }
+    }
+    if (lane == 0 && self_w != nullptr) self_w[t] = idw;
+  }
+  __syncthreads();
+  if (act == nullptr) return;
+  const long n = static_cast<long>(n_real) * ff;
+  for (long idx = threadIdx.x; idx < n; idx += blockDim.x) {
+    const int e = static_cast<int>(idx / ff), c = static_cast<int>(idx - static_cast<long>(e) * ff);
+    const float w = wsel[e];
+    float v = 0.f;
+    if (w != 0.f) {
+      const float gt = gu[t * sgu + static_cast<long>(e) * 2 * ff + c], up = gu[t * sgu + static_cast<long>(e) * 2 * ff + ff + c];
+      v = w * (gt * sigmoidf_(gt) * up);
+    }
+    st(act, t * sa + idx, v);
+  }
+}
+
 template <typename OT>
 __global__ void act_cols_kernel(const float* __restrict__ in, long si, OT* __restrict__ out, long so, int act, long T, int C) {
   const long n = T * C;
@@ -559,6 +775,89 @@ cudaError_t nrl_moe_route(const float* router, long sr, const float* router_bias
   else
     moe_route_kernel<__nv_bfloat16><<<T, th, smem, s>>>(router, sr, router_bias, E, top, gu, sgu, ff, static_cast<__nv_bfloat16*>(act),
                                                         sa, ids, wts);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_embed_norm(const void* embed, int w_f32, const int* tok, const float* w, float eps, float* x, void* h, int h_f32, int T,
+                           int W, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  const int th = W >= 1024 ? 256 : 128;
+#define NRL_EN(WT_, HT_) embed_norm_kernel<WT_, HT_><<<T, th, 0, s>>>(static_cast<const WT_*>(embed), tok, w, eps, x, static_cast<HT_*>(h), W)
+  if (w_f32 && h_f32) NRL_EN(float, float);
+  else if (w_f32) NRL_EN(float, __nv_bfloat16);
+  else if (h_f32) NRL_EN(__nv_bfloat16, float);
+  else NRL_EN(__nv_bfloat16, __nv_bfloat16);
+#undef NRL_EN
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_post_norm_residual(float* x, const float* o, const float* self_w, const float* w_post, const float* w_pre, float eps,
+                                   void* h, int h_f32, int T, int W, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (o == nullptr || w_post == nullptr || W < 1 || W > 12 * 1024) return cudaErrorInvalidValue;
+  const bool vec = W % 4 == 0 && aligned(x, 16) && aligned(o, 16) && aligned(w_post, 16) && (w_pre == nullptr || aligned(w_pre, 16)) &&
+                   (h == nullptr || aligned(h, h_f32 ? 16 : 8));
+  const int per = vec ? W / 4 : W;
+  const int th = per <= 64 ? 64 : per <= 128 ? 128 : 256;
+  const size_t smem = sizeof(float) * W;
+#define NRL_PN(HT_, V_) post_norm_residual_kernel<HT_, V_><<<T, th, smem, s>>>(x, o, self_w, w_post, w_pre, eps, static_cast<HT_*>(h), W)
+  if (h_f32) {
+    if (vec) NRL_PN(float, 4);
+    else NRL_PN(float, 1);
+  } else {
+    if (vec) NRL_PN(__nv_bfloat16, 4);
+    else NRL_PN(__nv_bfloat16, 1);
+  }
+#undef NRL_PN
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_side_gate(const float* u, long su, const void* table, long st_, int w_f32, int col0, const int* tok, void* out, long so,
+                          int out_f32, int T, int C, int Cpad, cudaStream_t s) {
+  if (T <= 0 || Cpad <= 0) return cudaSuccess;
+  if (C > Cpad) return cudaErrorInvalidValue;
+  const long n = static_cast<long>(T) * Cpad;
+  const int blocks = static_cast<int>((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+#define NRL_SG(WT_, OT_) side_gate_kernel<WT_, OT_><<<blocks, 256, 0, s>>>(u, su, static_cast<const WT_*>(table), st_, col0, tok, static_cast<OT_*>(out), so, T, C, Cpad)
+  if (w_f32 && out_f32) NRL_SG(float, float);
+  else if (w_f32) NRL_SG(float, __nv_bfloat16);
+  else if (out_f32) NRL_SG(__nv_bfloat16, float);
+  else NRL_SG(__nv_bfloat16, __nv_bfloat16);
+#undef NRL_SG
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_swiglu_cols(const float* in, long si, const float* rgate, long srg, void* out, long so, int out_f32, int T, int C,
+                            cudaStream_t s) {
+  if (T <= 0 || C <= 0) return cudaSuccess;
+  if (C % 4 == 0 && si % 4 == 0 && so % 4 == 0 && aligned(in, 16) && aligned(out, out_f32 ? 16 : 8)) {
+    const long n4 = static_cast<long>(T) * (C / 4);
+    const int blocks4 = static_cast<int>((n4 + 255) / 256 < 148 * 16 ? (n4 + 255) / 256 : 148 * 16);
+    if (out_f32) swiglu_cols_vec4_kernel<float><<<blocks4, 256, 0, s>>>(in, si, rgate, srg, static_cast<float*>(out), so, T, C / 4);
+    else swiglu_cols_vec4_kernel<__nv_bfloat16><<<blocks4, 256, 0, s>>>(in, si, rgate, srg, static_cast<__nv_bfloat16*>(out), so, T, C / 4);
+    return cudaGetLastError();
+  }
+  const long n = static_cast<long>(T) * C;
+  const int blocks = static_cast<int>((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (out_f32) swiglu_cols_kernel<float><<<blocks, 256, 0, s>>>(in, si, rgate, srg, static_cast<float*>(out), so, T, C);
+  else swiglu_cols_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(in, si, rgate, srg, static_cast<__nv_bfloat16*>(out), so, T, C);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_moe_route_all(const float* router, long sr, const float* correction, int E, int n_real, int top, float route_scale,
+                              const float* gu, long sgu, int ff, void* act, long sa, int act_f32, int* ids, float* wts, float* self_w,
+                              int T, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (E < 1 || top < 1 || top > E || top > 64 || E > 4096 || n_real < 0 || n_real > E || (n_real < E && self_w == nullptr))
+    return cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * 3 * E;
+  const int th = act == nullptr ? 32 : 256;
+  if (act_f32)
+    moe_route_all_kernel<float><<<T, th, smem, s>>>(router, sr, correction, E, n_real, top, route_scale, gu, sgu, ff,
+                                                    static_cast<float*>(act), sa, ids, wts, self_w);
+  else
+    moe_route_all_kernel<__nv_bfloat16><<<T, th, smem, s>>>(router, sr, correction, E, n_real, top, route_scale, gu, sgu, ff,
+                                                            static_cast<__nv_bfloat16*>(act), sa, ids, wts, self_w);
   return cudaGetLastError();
 }
 
