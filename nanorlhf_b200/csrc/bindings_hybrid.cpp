@@ -137,14 +137,14 @@ void delta_prep(Tensor qkv, int64_t col_k, const Tensor& b_raw, const Tensor& a_
         "delta_prep");
 }
 
-void delta_scan(const Tensor& qkv, int64_t col_k, int64_t col_v, const Tensor& beta, const Tensor& decay, Tensor state, Tensor o,
+void delta_scan(const Tensor& qkv, int64_t col_k, int64_t col_v, const c10::optional<Tensor>& beta, const Tensor& decay, Tensor state, Tensor o,
                 const Tensor& cu, const Tensor& start, const Tensor& state_slot, int64_t kv_heads, bool per_channel, int64_t impl) {
   c10::cuda::CUDAGuard guard(o.device());
   TORCH_CHECK(state.dim() == 4 && state.is_contiguous(), "delta_scan: state [slots, heads, D, Dv]");
   const int heads = static_cast<int>(state.size(1)), D = static_cast<int>(state.size(2)), Dv = static_cast<int>(state.size(3));
   const int E = static_cast<int>(start.numel());
   TORCH_CHECK(qkv.dim() == 2 && col_v + heads * Dv <= qkv.size(1) && o.is_contiguous() && o.size(-1) == heads * Dv, "delta_scan: shapes");
-  check(nrl_delta_scan(f32(qkv, "qkv"), qkv.stride(0), static_cast<int>(col_k), static_cast<int>(col_v), f32(beta, "beta"),
+  check(nrl_delta_scan(f32(qkv, "qkv"), qkv.stride(0), static_cast<int>(col_k), static_cast<int>(col_v), beta.has_value() ? f32(*beta, "beta") : nullptr,
                        f32(decay, "decay"), f32w(state, "state"), f32w(o, "o"), i32(cu, "cu"), i32(start, "start"),
                        i32(state_slot, "state_slot"), E, heads, static_cast<int>(kv_heads), D, Dv, per_channel ? 1 : 0,
                        static_cast<int>(impl), cur_stream()),
@@ -172,15 +172,31 @@ void qknorm_kv_write(Tensor q, const Tensor& k, const Tensor& v, const Tensor& q
 void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table, const Tensor& tok_entry,
                       const Tensor& pos, int64_t window, double scale, double out_scale, Tensor out, int64_t impl, bool chunked,
                       const c10::optional<Tensor>& head_scale, const c10::optional<Tensor>& head_slope,
-                      const c10::optional<Tensor>& gate) {
-  const bool single_token = block_table.size(0) == q.size(0);
+                      const c10::optional<Tensor>& gate, const c10::optional<Tensor>& head_sink, bool kv_shared, int64_t value_size,
+                      int64_t heads) {
+  const bool single_token = block_table.size(0) == (q.dim() == 3 ? q.size(1) : q.size(0));
   c10::cuda::CUDAGuard guard(q.device());
   const int Hkv = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
-  const int Dv = static_cast<int>(v_cache.size(3));
-  const int T = static_cast<int>(q.size(0)), Hq = static_cast<int>(q.size(1) / D);
+  // kv_shared: the values are the first `value_size` columns of the key rows (one cache tensor, passed twice)
+  const int Dv = kv_shared ? static_cast<int>(value_size) : static_cast<int>(v_cache.size(3));
+  // q [T, Hq * D], or head-major [Hq, T, D'] (D' >= D columns per row, `heads` = Hq given): the layout a batched GEMM leaves
+  const bool head_major = q.dim() == 3;
+  const int T = static_cast<int>(head_major ? q.size(1) : q.size(0)), Hq = static_cast<int>(head_major ? q.size(0) : q.size(1) / D);
   TORCH_CHECK(block_table.dim() == 2 && out.dim() == 2 && out.size(0) == T && out.size(1) == static_cast<int64_t>(Hq) * Dv,
               "window_attention: shapes");
-  NrlAttnMods md = {chunked ? 1 : 0, nullptr, nullptr, nullptr, 0};
+  NrlAttnMods md = {chunked ? 1 : 0, nullptr, nullptr, nullptr, 0, nullptr, 0, 0};
+  if (head_major) {
+    TORCH_CHECK(kv_shared && heads == Hq && q.size(2) >= D && q.stride(2) == 1 && q.stride(1) >= D, "window_attention: head-major queries [Hq, T, >= D] go with shared rows");
+    md.q_head_stride = q.stride(0);
+  }
+  if (kv_shared) {
+    TORCH_CHECK(v_cache.data_ptr() == k_cache.data_ptr() && Dv >= 1 && Dv <= D, "window_attention: shared rows need one cache and value_size <= D");
+    md.kv_shared = 1;
+  }
+  if (head_sink.has_value()) {
+    TORCH_CHECK(head_sink->numel() == Hq && head_sink->is_contiguous(), "window_attention: head_sink [Hq]");
+    md.head_sink = f32(*head_sink, "head_sink");
+  }
   if (head_scale.has_value()) {
     TORCH_CHECK(head_scale->numel() == Hq && head_scale->is_contiguous(), "window_attention: head_scale [Hq]");
     md.head_scale = f32(*head_scale, "head_scale");
@@ -198,11 +214,16 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   int nsplit = 0;
   Tensor part;
   if (single_token && (impl == 0 || impl == 3) && k_cache.scalar_type() == at::kBFloat16 &&
-      nrl_window_attention_mma_fits(out.data_ptr(), out.stride(0), Hq, Hkv, D, Dv, page)) {
+      nrl_window_attention_mma_fits(out.data_ptr(), out.stride(0), Hq, Hkv, D, Dv, page) && md.head_sink == nullptr && !md.kv_shared) {
     nsplit = nrl_window_attention_splits(T, Hq, Hkv, static_cast<int>(window), static_cast<int>(block_table.size(1)), page);
     if (nsplit >= 1) part = at::empty({T, Hq, 4 * nsplit, Dv + 2}, q.options().dtype(at::kFloat));
   }
-  check(nrl_window_attention(f32(q, "q"), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), typed(k_cache, "k_cache"),
+  if (single_token && (impl == 0 || impl == 3) && k_cache.scalar_type() == at::kBFloat16 && md.kv_shared && Hkv == 1 &&
+      window >= (1 << 30) && nrl_latent_attention_mma_fits(out.data_ptr(), out.stride(0), D, Dv, page)) {
+    nsplit = nrl_latent_attention_splits(T, Hq, Dv, static_cast<int>(block_table.size(1)));
+    part = at::empty({T, Hq, 4 * nsplit, Dv + 2}, q.options().dtype(at::kFloat));
+  }
+  check(nrl_window_attention(f32(q, "q"), head_major ? q.stride(1) : q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), typed(k_cache, "k_cache"),
                              i32(block_table, "block_table"), static_cast<int>(block_table.size(1)), i32(tok_entry, "tok_entry"),
                              i32(pos, "pos"), static_cast<int>(window), static_cast<float>(scale), static_cast<float>(out_scale),
                              out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, static_cast<int>(impl),
@@ -290,8 +311,118 @@ void moe_route(const Tensor& router, const c10::optional<Tensor>& router_bias, i
         "moe_route");
 }
 
+// ---- stream with the norm on the sublayer's output, token-side input, softmax-over-all routing ----
+void embed_norm(const Tensor& embed, const Tensor& tok, const Tensor& w, double eps, Tensor x, Tensor h) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const int T = static_cast<int>(tok.numel()), W = static_cast<int>(embed.size(1));
+  TORCH_CHECK(embed.dim() == 2 && embed.is_contiguous() && x.is_contiguous() && h.is_contiguous() && x.size(0) >= T && x.size(1) == W &&
+                  h.size(0) >= T && h.size(1) == W && w.numel() == W, "embed_norm: shapes");
+  check(nrl_embed_norm(embed.data_ptr(), typed(embed, "embed"), i32(tok, "tok"), f32(w, "w"), static_cast<float>(eps), f32w(x, "x"),
+                       h.data_ptr(), typed(h, "h"), T, W, cur_stream()),
+        "embed_norm");
+}
+
+void post_norm_residual(Tensor x, const Tensor& o, const c10::optional<Tensor>& self_w, const Tensor& w_post,
+                        const c10::optional<Tensor>& w_pre, double eps, const c10::optional<Tensor>& h) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous(), "post_norm_residual: x [T, W] contiguous");
+  const int T = static_cast<int>(x.size(0)), W = static_cast<int>(x.size(1));
+  TORCH_CHECK(o.is_contiguous() && o.dim() == 2 && o.size(0) == T && o.size(1) == W && w_post.numel() == W, "post_norm_residual: o / w_post");
+  if (self_w.has_value()) TORCH_CHECK(self_w->is_contiguous() && self_w->numel() == T, "post_norm_residual: self_w [T]");
+  if (w_pre.has_value()) TORCH_CHECK(w_pre->numel() == W && h.has_value(), "post_norm_residual: w_pre [W] goes with h");
+  if (h.has_value()) TORCH_CHECK(h->is_contiguous() && h->size(0) == T && h->size(1) == W, "post_norm_residual: h [T, W]");
+  check(nrl_post_norm_residual(f32w(x, "x"), f32(o, "o"), self_w.has_value() ? f32(*self_w, "self_w") : nullptr, f32(w_post, "w_post"),
+                               w_pre.has_value() ? f32(*w_pre, "w_pre") : nullptr, static_cast<float>(eps),
+                               h.has_value() ? h->data_ptr() : nullptr, h.has_value() ? typed(*h, "h") : 1, T, W, cur_stream()),
+        "post_norm_residual");
+}
+
+void side_gate(const Tensor& u, const Tensor& table, int64_t col0, const Tensor& tok, Tensor out, int64_t C) {
+  c10::cuda::CUDAGuard guard(u.device());
+  const int T = static_cast<int>(u.size(0));
+  TORCH_CHECK(u.dim() == 2 && u.size(1) >= C && table.dim() == 2 && col0 >= 0 && col0 + C <= table.size(1) && out.dim() == 2 &&
+                  out.size(0) == T && out.size(1) >= C && tok.numel() >= T, "side_gate: shapes");
+  f32(u, "u");
+  check(nrl_side_gate(u.data_ptr<float>(), u.stride(0), table.data_ptr(), table.stride(0), typed(table, "table"), static_cast<int>(col0),
+                      i32(tok, "tok"), out.data_ptr(), out.stride(0), typed(out, "out"), T, static_cast<int>(C),
+                      static_cast<int>(out.size(1)), cur_stream()),
+        "side_gate");
+}
+
+void swiglu_cols(const Tensor& in, const c10::optional<Tensor>& rgate, Tensor out) {
+  c10::cuda::CUDAGuard guard(in.device());
+  TORCH_CHECK(in.dim() == 2 && out.dim() == 2 && in.size(0) == out.size(0) && in.size(1) == 2 * out.size(1), "swiglu_cols: in [T, 2 C], out [T, C]");
+  if (rgate.has_value()) TORCH_CHECK(rgate->dim() == 2 && rgate->size(0) == in.size(0) && rgate->size(1) == 1, "swiglu_cols: rgate [T, 1]");
+  check(nrl_swiglu_cols(f32(in, "in"), in.stride(0), rgate.has_value() ? f32(*rgate, "rgate") : nullptr,
+                        rgate.has_value() ? rgate->stride(0) : 0, out.data_ptr(), out.stride(0), typed(out, "out"),
+                        static_cast<int>(in.size(0)), static_cast<int>(out.size(1)), cur_stream()),
+        "swiglu_cols");
+}
+
+void moe_route_all(const Tensor& router, const c10::optional<Tensor>& correction, int64_t n_real, int64_t top, double route_scale,
+                   const c10::optional<Tensor>& gu, int64_t ff, const c10::optional<Tensor>& act, const c10::optional<Tensor>& ids,
+                   const c10::optional<Tensor>& wts, const c10::optional<Tensor>& self_w) {
+  c10::cuda::CUDAGuard guard(router.device());
+  TORCH_CHECK(router.dim() == 2, "moe_route_all: router [T, E]");
+  const int T = static_cast<int>(router.size(0)), E = static_cast<int>(router.size(1));
+  if (correction.has_value()) TORCH_CHECK(correction->numel() == E, "moe_route_all: correction [E]");
+  TORCH_CHECK(act.has_value() == gu.has_value(), "moe_route_all: gu and act go together");
+  if (act.has_value())
+    TORCH_CHECK(gu->dim() == 2 && gu->size(0) == T && gu->size(1) == n_real * 2 * ff && act->dim() == 2 && act->size(0) == T &&
+                    act->size(1) == n_real * ff, "moe_route_all: gu [T, n_real*2ff], act [T, n_real*ff]");
+  if (ids.has_value()) TORCH_CHECK(ids->scalar_type() == torch::kInt32 && ids->is_contiguous() && ids->numel() == static_cast<int64_t>(T) * top, "moe_route_all: ids int32 [T, top]");
+  if (wts.has_value()) TORCH_CHECK(wts->is_contiguous() && wts->numel() == static_cast<int64_t>(T) * top, "moe_route_all: wts float [T, top]");
+  if (self_w.has_value()) TORCH_CHECK(self_w->is_contiguous() && self_w->numel() == T, "moe_route_all: self_w float [T]");
+  Tensor wt = wts.has_value() ? *wts : Tensor(), sw = self_w.has_value() ? *self_w : Tensor();
+  check(nrl_moe_route_all(f32(router, "router"), router.stride(0), correction.has_value() ? f32(*correction, "correction") : nullptr, E,
+                          static_cast<int>(n_real), static_cast<int>(top), static_cast<float>(route_scale),
+                          gu.has_value() ? f32(*gu, "gu") : nullptr, gu.has_value() ? gu->stride(0) : 0, static_cast<int>(ff),
+                          act.has_value() ? act->data_ptr() : nullptr, act.has_value() ? act->stride(0) : 0,
+                          act.has_value() ? typed(*act, "act") : 1, ids.has_value() ? ids->data_ptr<int>() : nullptr,
+                          wts.has_value() ? f32w(wt, "wts") : nullptr, self_w.has_value() ? f32w(sw, "self_w") : nullptr, T, cur_stream()),
+        "moe_route_all");
+}
+
+void gla_prep(Tensor qkv, const Tensor& a_raw, const c10::optional<Tensor>& a_bias, double tau, Tensor decay, int64_t heads, int64_t D) {
+  c10::cuda::CUDAGuard guard(qkv.device());
+  const int T = static_cast<int>(qkv.size(0));
+  const int64_t n = heads * D;
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) >= n && a_raw.dim() == 2 && a_raw.size(0) == T && a_raw.size(1) == n && decay.is_contiguous() &&
+                  decay.numel() == static_cast<int64_t>(T) * n, "gla_prep: shapes");
+  if (a_bias.has_value()) TORCH_CHECK(a_bias->numel() == n, "gla_prep: a_bias [heads * D]");
+  check(nrl_gla_prep(f32w(qkv, "qkv"), qkv.stride(0), f32(a_raw, "a_raw"), a_raw.stride(0), a_bias.has_value() ? f32(*a_bias, "a_bias") : nullptr,
+                     static_cast<float>(tau), f32w(decay, "decay"), T, static_cast<int>(heads), static_cast<int>(D), cur_stream()),
+        "gla_prep");
+}
+
+void latent_kv_write(const Tensor& q, int64_t H, int64_t dn, int64_t dr, const Tensor& dkv, const Tensor& w, double eps, const Tensor& freq,
+                     int64_t rdims, double mult, bool interleaved, const Tensor& pos, const Tensor& kv_slot, Tensor cache, Tensor qa,
+                     const c10::optional<Tensor>& qn) {
+  c10::cuda::CUDAGuard guard(q.device());
+  const int T = static_cast<int>(q.size(0));
+  const int64_t rank = w.numel(), D = rank + dr;
+  TORCH_CHECK(cache.dim() == 4 && cache.is_contiguous() && cache.size(1) == 1 && cache.size(3) == D, "latent_kv_write: cache [pages, 1, page, rank + dr]");
+  TORCH_CHECK(q.dim() == 2 && q.size(1) == H * (dn + dr) && dkv.dim() == 2 && dkv.size(0) == T && dkv.size(1) == D && pos.numel() >= T &&
+                  kv_slot.numel() >= T, "latent_kv_write: shapes");
+  // qa: [T, H * D], or head-major [H, T, D]
+  TORCH_CHECK((qa.dim() == 2 && qa.size(0) == T && qa.size(1) == H * D) ||
+                  (qa.dim() == 3 && qa.size(0) == H && qa.size(1) == T && qa.size(2) == D && qa.stride(2) == 1), "latent_kv_write: qa [T, H * D] or [H, T, D]");
+  const long sqa = qa.dim() == 3 ? qa.stride(1) : qa.stride(0), sha = qa.dim() == 3 ? qa.stride(0) : D;
+  if (qn.has_value())
+    TORCH_CHECK(qn->scalar_type() == torch::kBFloat16 && qn->is_contiguous() && qn->numel() == static_cast<int64_t>(H) * T * dn,
+                "latent_kv_write: qn bf16 [H, T, dn]");
+  TORCH_CHECK(freq.is_cuda() && freq.scalar_type() == torch::kFloat64 && freq.is_contiguous() && freq.numel() == rdims / 2 && rdims % 2 == 0 &&
+                  rdims <= dr, "latent_kv_write: freq double [rdims / 2]");
+  check(nrl_latent_kv_write(f32(q, "q"), q.stride(0), static_cast<int>(H), static_cast<int>(dn), static_cast<int>(dr), f32(dkv, "dkv"),
+                            dkv.stride(0), static_cast<int>(rank), f32(w, "w"), static_cast<float>(eps), freq.data_ptr<double>(),
+                            static_cast<int>(rdims), static_cast<float>(mult), interleaved ? 1 : 0, i32(pos, "pos"), i32(kv_slot, "kv_slot"),
+                            cache.data_ptr(), typed(cache, "cache"), static_cast<int>(cache.size(2)), f32w(qa, "qa"), sqa, sha,
+                            qn.has_value() ? qn->data_ptr() : nullptr, T, cur_stream()),
+        "latent_kv_write");
+}
+
 // ---- mixture of experts, grouped form ----
-std::vector<Tensor> moe_plan(const Tensor& ids, int64_t E, int64_t tile_rows) {
+std::vector<Tensor> moe_plan(const Tensor& ids, int64_t E, int64_t tile_rows, int64_t n_real) {
   c10::cuda::CUDAGuard guard(ids.device());
   TORCH_CHECK(ids.dim() == 2 && ids.scalar_type() == torch::kInt32 && ids.is_contiguous(), "moe_plan: ids int32 [T, top]");
   const int R = static_cast<int>(ids.numel()), top = static_cast<int>(ids.size(1));
@@ -299,7 +430,7 @@ std::vector<Tensor> moe_plan(const Tensor& ids, int64_t E, int64_t tile_rows) {
   auto opt = ids.options();
   Tensor slot_of = at::empty({R}, opt), row_token = at::empty({R}, opt), seg = at::empty({E + 1}, opt);
   Tensor tiles = at::zeros({max_tiles, 3}, opt), num_tiles = at::zeros({1}, opt);
-  check(nrl_moe_plan(i32(ids, "ids"), R, top, static_cast<int>(E), static_cast<int>(tile_rows), slot_of.data_ptr<int>(),
+  check(nrl_moe_plan(i32(ids, "ids"), R, top, static_cast<int>(E), static_cast<int>(n_real < 0 ? E : n_real), static_cast<int>(tile_rows), slot_of.data_ptr<int>(),
                      row_token.data_ptr<int>(), seg.data_ptr<int>(), tiles.data_ptr<int>(), num_tiles.data_ptr<int>(), cur_stream()),
         "moe_plan");
   return {slot_of, row_token, seg, tiles, num_tiles};
@@ -382,13 +513,21 @@ void gemm_tc_grouped(const Tensor& a, const Tensor& b, const c10::optional<Tenso
 
 namespace nrl {
 void bind_hybrid(pybind11::module_& m) {
-  m.def("moe_plan", &moe_plan, "sort (token, choice) pairs by expert: slot_of, row_token, seg, tiles, num_tiles");
+  m.def("moe_plan", &moe_plan, "sort (token, choice) pairs by expert: slot_of, row_token, seg, tiles, num_tiles (experts >= n_real get no tiles)",
+        pybind11::arg("ids"), pybind11::arg("E"), pybind11::arg("tile_rows"), pybind11::arg("n_real") = -1);
   m.def("gather_rows", &gather_rows, "out[r] = in[row_token[r]] (bf16 rows)");
   m.def("swiglu_rows", &swiglu_rows, "act = silu(gu[:, :ff]) * gu[:, ff:] (float in, bf16 out)");
   m.def("moe_combine", &moe_combine, "out[t] = sum_k wts[t, k] y[slot_of[t, k]]");
   m.def("gemm_tc_grouped", &gemm_tc_grouped, "grouped tcgen05 GEMM over rows sorted by expert: float32 out, or fused SwiGLU bf16 out",
         pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("out"), pybind11::arg("tiles"), pybind11::arg("num_tiles"),
         pybind11::arg("block_n") = 0, pybind11::arg("act") = pybind11::none());
+  m.def("embed_norm", &embed_norm, "x = rmsnorm(embed[tok]) * w (float), h = x (typed)");
+  m.def("post_norm_residual", &post_norm_residual, "x += rmsnorm(o + self_w x) * w_post; h = w_pre ? rmsnorm(x) * w_pre : x");
+  m.def("side_gate", &side_gate, "out = gelu_tanh(u) * table[tok, col0:col0 + C], zero padded");
+  m.def("swiglu_cols", &swiglu_cols, "out = silu(in[:, :C]) * in[:, C:] * sigmoid(row gate)");
+  m.def("moe_route_all", &moe_route_all, "routing by a softmax over all router outputs, with identity experts");
+  m.def("gla_prep", &gla_prep, "q * D^-1/2 in place and per-channel decays sigmoid(z)^(1/tau) of gated linear attention");
+  m.def("latent_kv_write", &latent_kv_write, "normed latent + rotated shared key part into the page; rotated query parts into the absorbed queries");
   m.def("embed_pos", &embed_pos, "x0 = embed[tok] + pos_table[pos] (float)");
   m.def("stream_norm", &stream_norm, "close a layer, form the depth-weighted stream and its single-gain RMS norm");
   m.def("act_cols", &act_cols, "typed out = act(float in): 0 copy, 1 relu^2");
@@ -405,7 +544,8 @@ void bind_hybrid(pybind11::module_& m) {
         pybind11::arg("k_cache"), pybind11::arg("v_cache"), pybind11::arg("block_table"), pybind11::arg("tok_entry"), pybind11::arg("pos"),
         pybind11::arg("window"), pybind11::arg("scale"), pybind11::arg("out_scale"), pybind11::arg("out"), pybind11::arg("impl") = 0,
         pybind11::arg("chunked") = false, pybind11::arg("head_scale") = pybind11::none(), pybind11::arg("head_slope") = pybind11::none(),
-        pybind11::arg("gate") = pybind11::none());
+        pybind11::arg("gate") = pybind11::none(), pybind11::arg("head_sink") = pybind11::none(), pybind11::arg("kv_shared") = false,
+        pybind11::arg("value_size") = 0, pybind11::arg("heads") = 0);
   m.def("kv_write_blend", &kv_write_blend, "keys and (optionally blended) values of a step's tokens into their pages");
   m.def("embed_hashed", &embed_hashed, "x0 = embed[tok] * scale + pair[hash(previous token, token)] (float), previous tokens carried per slot");
   m.def("group_norm_residual", &group_norm_residual, "x += groupnorm(o * sigmoid(gate)) * w_post; h = groupnorm(x) * w_pre");

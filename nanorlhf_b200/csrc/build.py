@@ -22,10 +22,10 @@ OBJ = os.path.join(HERE, "build")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 CU_SOURCES = ["gemm_sm100.cu", "gemm_sm100_2cta.cu", "gemm_tc.cu", "elementwise.cu", "rl_kernels.cu", "sampling.cu", "attention_decode.cu", "attention_decode_fp8.cu", "rope_kv.cu", "attention_fwd_tc.cu", "attention_bwd_tc.cu",
-              "attention_varlen.cu", "comm.cu", "quant.cu", "stream_ops.cu", "recurrent.cu", "attention_window.cu", "attention_window_mma.cu", "moe.cu"]
+              "attention_varlen.cu", "comm.cu", "quant.cu", "stream_ops.cu", "recurrent.cu", "attention_window.cu", "attention_window_mma.cu", "attention_latent_mma.cu", "moe.cu"]
 CPP_SOURCES = ["bindings.cpp", "runtime.cpp", "bindings_hybrid.cpp"]
 # kernels of the float32 serving mode: IEEE division / sqrt / exp (no --use_fast_math)
-PRECISE_SOURCES = {"stream_ops.cu", "recurrent.cu", "attention_window.cu", "attention_window_mma.cu", "moe.cu"}
+PRECISE_SOURCES = {"stream_ops.cu", "recurrent.cu", "attention_window.cu", "attention_window_mma.cu", "attention_latent_mma.cu", "moe.cu"}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 if os.environ.get("NRL_ATTN_PROFILE") == "1":       # cycle accounting build of attention_fwd_tc.cu (bench/attn_prof.py)

@@ -60,6 +60,7 @@ def delta_prep(qkv, col_k, b_raw, a_raw, dt_bias, A_log, beta, decay, kv_heads, 
 
 
 def delta_scan(qkv, col_k, col_v, beta, decay, state, o, plan, kv_heads, per_channel, impl: str = "auto"):
+    """``beta`` None: plain accumulation ``S = diag(decay) S + k v^T`` (gated linear attention) instead of the delta rule."""
     native._count()
     _ext().delta_scan(qkv, col_k, col_v, beta, decay, state, o, plan.cu, plan.start, plan.state_slot, kv_heads, per_channel,
                       SCAN_IMPLS[impl])
@@ -74,14 +75,18 @@ WINDOW_IMPLS = {"auto": 0, "tile": 1, "simple": 2, "mma": 3}
 
 
 def window_attention(q, k_cache, v_cache, plan, window, scale, out_scale, out, impl: str = "auto", chunked: bool = False,
-                     head_scale=None, head_slope=None, gate=None):
+                     head_scale=None, head_slope=None, gate=None, head_sink=None, value_size: int = 0):
     """``impl``: "auto" (tensor cores for prompt portions over bf16 pages, the scalar tile kernel otherwise) or one kernel by
     name; a kernel that does not fit the shapes raises.  ``chunked``: keys of the query's own chunk of ``window`` positions
     instead of the last ``window`` keys.  ``head_scale`` / ``head_slope`` [heads]: per-head score multiplier and linear distance
-    penalty; ``gate`` [T, heads]: the head's output is multiplied by sigmoid(gate)."""
+    penalty; ``gate`` [T, heads]: the head's output is multiplied by sigmoid(gate); ``head_sink`` [heads]: the softmax denominator
+    also holds exp(sink).  ``value_size`` > 0 (with ``v_cache is k_cache``): the values are the first ``value_size`` columns of the
+    key rows (latent attention: one cached row per token serves as key and value of every head); ``q`` may then be head-major
+    [heads, T, >= D], the layout a batched GEMM leaves."""
     native._count()
     _ext().window_attention(q, k_cache, v_cache, plan.block_table, plan.tok_entry, plan.pos, window, scale, out_scale, out,
-                            WINDOW_IMPLS[impl], chunked, head_scale, head_slope, gate)
+                            WINDOW_IMPLS[impl], chunked, head_scale, head_slope, gate, head_sink, value_size > 0, value_size,
+                            q.shape[0] if q.dim() == 3 else 0)
 
 
 def kv_write_blend(k, v, v_other, lam, k_cache, v_cache, plan):
@@ -118,17 +123,19 @@ def interleave_gate_up(gate, up):
     return torch.stack([gate.view(ff // 32, 32, W), up.view(ff // 32, 32, W)], 1).reshape(2 * ff, W)
 
 
-def moe_grouped_ffn(h, ids, wts, w_gate_up, w_down, experts, ff, out, fused_act: bool = False):
+def moe_grouped_ffn(h, ids, wts, w_gate_up, w_down, experts, ff, out, fused_act: bool = False, identity: int = 0):
     """Expert feed-forwards of a routed batch on the grouped tcgen05 GEMM.  ``h`` bf16 [T, W]; ``ids`` / ``wts`` [T, top] from
     ``moe_route``; ``w_gate_up`` bf16 [experts * 2 ff, W] (per expert its gate rows, then its up rows; ``fused_act``: interleaved
     per 32 features by ``interleave_gate_up``, the SwiGLU is then formed in the GEMM's epilogue); ``w_down`` bf16
-    [experts * W, ff]; ``out`` float [T, W] = sum_k wts[t, k] * expert_k(h[t]).  No launch depends on the routing."""
+    [experts * W, ff]; ``out`` float [T, W] = sum_k wts[t, k] * expert_k(h[t]).  No launch depends on the routing.
+    ``identity``: ids ``experts .. experts + identity - 1`` name experts without matrices; their pairs carry weight 0 here and are
+    skipped (the caller adds their share of the input)."""
     import torch
     T, W = h.shape
     R = ids.numel()
     ext = _ext()
     native._count(5 if fused_act else 6)
-    slot_of, row_token, _seg, tiles, num_tiles = ext.moe_plan(ids, experts, 128)
+    slot_of, row_token, _seg, tiles, num_tiles = ext.moe_plan(ids, experts + identity, 128, experts)
     xp = torch.empty(R, W, dtype=h.dtype, device=h.device)
     ext.gather_rows(h, row_token, xp)
     act = torch.empty(R, ff, dtype=h.dtype, device=h.device)
@@ -142,3 +149,70 @@ def moe_grouped_ffn(h, ids, wts, w_gate_up, w_down, experts, ff, out, fused_act:
     ext.gemm_tc_grouped(act, w_down, y, tiles, num_tiles)
     ext.moe_combine(y, slot_of, wts, out)
     return out
+
+
+def embed_norm(embed, tok, w, eps, x, h):
+    """x = embed[tok] / rms * w (float); h = x in the GEMM operand type."""
+    native._count()
+    _ext().embed_norm(embed, tok, w, eps, x, h)
+
+
+def post_norm_residual(x, o, self_w, w_post, w_pre, eps, h):
+    """Boundary of a stream that norms only what a sublayer returns: ``x += rmsnorm(o + self_w[:, None] * x) * w_post`` (``self_w``
+    None: no such term), then ``h = rmsnorm(x) * w_pre`` or, without ``w_pre``, ``h = x`` (operand type)."""
+    native._count()
+    _ext().post_norm_residual(x, o, self_w, w_post, w_pre, eps, h)
+
+
+def side_gate(u, table, col0, tok, out, dim):
+    """out[:, :dim] = gelu_tanh(u[:, :dim]) * table[tok, col0:col0 + dim]; further columns of ``out`` are zeroed."""
+    native._count()
+    _ext().side_gate(u, table, col0, tok, out, dim)
+
+
+def swiglu_cols(gu, row_gate, out):
+    """out = silu(gu[:, :C]) * gu[:, C:] (``* sigmoid(row_gate)`` [T, 1] when given)."""
+    native._count()
+    _ext().swiglu_cols(gu, row_gate, out)
+
+
+def moe_route_all(router, correction, n_real, top, scale, gu=None, ff=0, act=None, ids=None, wts=None, self_w=None):
+    """Routing by a softmax over all router outputs (the last ``E - n_real`` are identity experts), choice by score + correction,
+    weights = chosen scores / their sum * scale; ``self_w`` [T] receives the identity experts' weights."""
+    native._count()
+    _ext().moe_route_all(router, correction, n_real, top, scale, gu, ff, act, ids, wts, self_w)
+
+
+def gla_prep(qkv, a_raw, a_bias, tau, decay, heads, dim):
+    """q (first heads * dim columns of ``qkv``) times dim^-1/2 in place; decay = sigmoid(a_raw + a_bias)^(1 / tau)."""
+    native._count()
+    _ext().gla_prep(qkv, a_raw, a_bias, tau, decay, heads, dim)
+
+
+def latent_kv_write(q, heads, dim, rot_dim, dkv, norm_w, eps, freq, rot_dims, mult, interleaved, plan, cache, qa, qn=None):
+    """Latent attention, write side: RMS-normed latent + rotated shared key part into the token's cache row, the heads' rotated
+    query parts into ``qa`` ([T, heads * (rank + rot_dim)] or head-major [heads, T, rank + rot_dim]) behind the absorbed columns;
+    ``qn`` (bf16 [heads, T, dim]) receives the unrotated query columns as the operand of the GEMM that absorbs them."""
+    native._count()
+    _ext().latent_kv_write(q, heads, dim, rot_dim, dkv, norm_w, eps, freq, rot_dims, mult, interleaved, plan.pos, plan.kv_slot, cache, qa, qn)
+
+
+def rotary_frequencies(dims: int, base: float, scaling=None):
+    """(frequencies [dims / 2] as float64 list, cos / sin multiplier).  ``scaling`` {"factor", "original", "fast", "slow"}: frequencies
+    that turn more than ``fast`` times within ``original`` positions keep their value, those that turn less than ``slow`` times
+    are divided by ``factor``, linear in the pair index between; cos and sin are then multiplied by 0.1 ln(factor) + 1."""
+    import math
+    f = [base ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if not scaling:
+        return f, 1.0
+    factor, orig = float(scaling["factor"]), float(scaling["original"])
+
+    def pair_of(turns):                                    # the (real-valued) pair index that turns `turns` times in `orig` positions
+        return dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+    lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair_of(float(scaling["slow"]))), dims - 1)
+    out = []
+    for i, fi in enumerate(f):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(fi / factor * ramp + fi * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
