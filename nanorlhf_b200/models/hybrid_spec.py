@@ -19,7 +19,8 @@ from .hf_io import load_state_dict, save_state_dict
 
 @dataclass
 class MixerSpec:
-    """One token mixer of a layer.  ``kind``: window_attention | conv_attention | ssd | gated_delta.  ``prefix``: tensor-name prefix."""
+    """One token mixer of a layer.  ``kind``: window_attention | conv_attention | ssd | gated_delta | latent_attention | gla.
+    ``prefix``: tensor-name prefix."""
     kind: str
     prefix: str
     out_scale: float = 1.0
@@ -39,6 +40,18 @@ class MixerSpec:
     head_gate: bool = False      # head output times sigmoid of a per-head projection of the mixer's input (tensor "g")
     v_blend: int = -1            # -1: none; else the layer whose values this layer's values are blended with (tensor "vmix"),
                                  # its own index for the layer that only provides them
+    # latent_attention (keys and values of all heads are projections "uk" / "uv" of one RMS-normed latent of `kv_rank` columns per
+    # token, plus one rotated key part of `rot_dim` columns shared by the heads; only the latent and that part are cached;
+    # `dim` is the unrotated query/key size per head; causal; `head_gate` and `head_sink` as below):
+    kv_rank: int = 0
+    rot_dim: int = 0             # rotated query/key columns per head, behind the `dim` unrotated ones
+    rot_dims: int = 0            # how many of the rot_dim columns turn (the rest pass unchanged)
+    rot_base: float = 10000.0    # frequency i of rot_dims / 2 is rot_base^(-2 i / rot_dims)
+    rot_layout: str = "interleaved"   # "interleaved": column 2i turns with 2i + 1;  "half": i with i + rot_dims / 2
+    rot_scaling: Optional[dict] = None  # frequency-dependent stretch {"factor", "original", "fast", "slow"} with its cos / sin multiplier
+    head_sink: bool = False      # the softmax denominator also holds exp(sink_h) (tensor "sink"): a score with no key and no value
+    # gla (gated linear attention, S = diag(decay) S + k v^T, o = S^T q D^-1/2; decay = sigmoid(a2 (a1 h) + a2.b)^(1 / tau) per key channel):
+    tau: float = 1.0
 
 
 @dataclass
@@ -47,9 +60,19 @@ class LayerSpec:
     mixers: List[MixerSpec]
     ff: int = 0                  # 0: no feed-forward; else its inner width (of one expert for "moe")
     ff_act: str = "relu2"        # "relu2": W_down relu(W_up h)^2;  "swiglu": W_down (silu(W_gate h) * W_up h)
-    ff_kind: str = "dense"       # "dense" | "moe" (experts e0.., top-k router with softmax over the chosen logits)
+    ff_kind: str = "dense"       # "dense" | "moe" (experts e0.., top-k router)
     experts: int = 0
     top: int = 0
+    route: str = "softmax_top"   # "softmax_top": the largest logits (+ bias "router.b"), weights = softmax over the chosen logits
+                                 # "softmax_all": scores = softmax over all router outputs, chosen by score + "correction",
+                                 #                weights = the chosen scores / their sum * route_scale
+    route_scale: float = 1.0
+    identity_experts: int = 0    # router outputs behind the `experts` real ones whose expert returns its input
+    shared_ff: int = 0           # > 0: a SwiGLU expert of this width for every token (tensors "shared.*")
+    shared_gate: bool = False    # its result times sigmoid(shared.sg h), one number per token
+    side_dim: int = 0            # > 0: per-layer token input after the feed-forward (stream kind "post_norm"): columns
+                                 # [index * side_dim, (index + 1) * side_dim) of the table "side.embed", gated by gelu_tanh(side.gate x),
+                                 # projected by side.proj, RMS-normed with side.norm and added
 
 
 @dataclass
@@ -59,7 +82,9 @@ class StreamSpec:
     ``kind`` "depth_weighted": every layer reads one single-gain RMS norm of a learned weighted sum of all earlier results and
     adds ``mixer + ff`` of it (tensors norm1, dwa).  ``kind`` "sandwich": ``x += norm1b(g1 * mixer(norm1 x))`` then
     ``x += norm2b(g2 * ff(norm2 x))`` with group RMS norms (a weight per column) and, when ``gated_residual``, sigmoid gates
-    ``g = sigmoid(rg h + rg.b)`` of the sublayer's input."""
+    ``g = sigmoid(rg h + rg.b)`` of the sublayer's input.  ``kind`` "post_norm": sublayers read the stream itself and only their
+    result is normed, ``x += norm1(mixer(x))`` then ``x += norm2(ff(x))`` (single-group RMS norms with a weight per column); the
+    embedding is normed too (tensor "embed.norm")."""
     kind: str = "depth_weighted"
     norm_groups: int = 1
     gated_residual: bool = False

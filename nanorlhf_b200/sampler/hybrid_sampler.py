@@ -17,6 +17,10 @@ step in a per-sequence slot) and it gives chunked prefill and continuous batchin
   sigmoid gate on the sublayer's result; the mixer and the feed-forward are two stages, each with its own pair of fused
   matrices); a mixture-of-experts feed-forward runs only the chosen experts, rows sorted by expert through a grouped
   tcgen05 GEMM (float32 serving: dense form on cuBLAS);
+* a third kind of stream, "post_norm", has sublayers that read the stream itself and norms only what they return; its
+  layers may end with a gated per-layer token input (a third stage); its mixers are latent attention (one cached latent row
+  per token serves all heads: queries are absorbed into the latent space before the paged attention kernel and the result
+  is expanded per head after it) and gated linear attention (the delta-rule scan without the delta);
 * the residual stream, its depth-weighted average, norms, scores, softmax, decays and recurrent state are float32 in both
   serving modes; ``dtype="bf16"`` keeps GEMM operands and KV pages in bf16 (fp32 accumulation, fp32 GEMM results),
   ``dtype="fp32"`` keeps everything in float32 with TF32 off;
@@ -58,14 +62,16 @@ class StepPlan:
 
 
 class _Mixer:
-    __slots__ = ("spec", "cols", "out_col", "out_size", "vec", "k_cache", "v_cache", "conv_state", "state", "w_lr2", "lr_cols", "rank")
+    __slots__ = ("spec", "cols", "out_col", "out_size", "vec", "k_cache", "v_cache", "conv_state", "state", "w_lr2", "lr_cols", "rank",
+                 "w_uk", "w_uv", "rot_mult")
 
 
 class _Layer:
     """One pair of fused matrices with what runs between them: a whole layer of a depth-weighted stream (mixers and the
     feed-forward side by side), or one sublayer of a sandwich stream (the mixer, or the feed-forward)."""
     __slots__ = ("spec", "gain", "dw", "w_in", "w_out", "mixers", "ff_col", "ff_out_col", "n_in", "k_out", "out_pad",
-                 "w_pre", "w_post", "gate_col", "gate_bias", "router_col", "router_bias", "w_gate_up", "w_down")
+                 "w_pre", "w_post", "gate_col", "gate_bias", "router_col", "router_bias", "w_gate_up", "w_down",
+                 "shared_col", "shared_out_col", "sg_col", "side_col", "side_out_col", "side_col0")
 
 
 def _pad8(n: int) -> int:
@@ -146,8 +152,23 @@ class HybridSampler:
                     L = self._build_stage(spec, mixers, ff, gate=p + "rg" + n if st.gated_residual else None)
                     L.w_pre, L.w_post = self._f(p + "norm" + n), self._f(p + "norm" + n + "b")
                     self.layers.append(L)
+            elif st.kind == "post_norm":                  # up to three stages: mixer, feed-forward, token input; only results are normed
+                L = self._build_stage(spec, spec.mixers, False)
+                L.w_post = self._f(p + "norm1")
+                self.layers.append(L)
+                if spec.ff:
+                    L = self._build_stage(spec, [], True)
+                    L.w_post = self._f(p + "norm2")
+                    self.layers.append(L)
+                if spec.side_dim:
+                    L = self._build_stage(spec, [], False, side=True)
+                    L.w_post = self._f(p + "side.norm")
+                    self.layers.append(L)
             else:
                 raise ValueError(f"unknown stream kind {st.kind!r}")
+        self.embed_gain = self._f("embed.norm") if st.kind == "post_norm" else None
+        self.side_table = (self._t("side.embed").to(device=dev, dtype=wd).contiguous()
+                           if st.kind == "post_norm" and lm.has_tensor("side.embed") else None)
         self.embed = self._t("embed").to(device=dev, dtype=wd).contiguous()
         self.pos_table = self._t("pos").to(device=dev, dtype=wd).contiguous() if st.positions else None
         self.pair_table = self._t("bigram").to(device=dev, dtype=wd).contiguous() if st.pair_buckets else None
@@ -157,7 +178,7 @@ class HybridSampler:
         self.head[:V] = self._t("head").to(device=dev, dtype=wd)
         self._weights_version = self.weights_fingerprint()
 
-    def _build_stage(self, spec, mixer_specs, with_ff: bool, gate: Optional[str] = None) -> _Layer:
+    def _build_stage(self, spec, mixer_specs, with_ff: bool, gate: Optional[str] = None, side: bool = False) -> _Layer:
         """Fuse every projection that reads the stage's normed input into ``w_in`` and every projection that writes the stream
         into ``w_out``; keep the small vectors as float32."""
         dev, wd, W = self.device, self.wdtype, self.cfg.width
@@ -166,6 +187,8 @@ class HybridSampler:
         L.spec = spec
         L.gain = L.dw = L.w_pre = L.w_post = L.gate_col = L.gate_bias = L.router_col = L.router_bias = None
         L.w_gate_up = L.w_down = None
+        L.shared_col = L.shared_out_col = L.sg_col = L.side_col = L.side_out_col = None
+        L.side_col0 = 0
         rows_in: List[torch.Tensor] = []
         cols_out: List[torch.Tensor] = []
         n_in = k_out = 0
@@ -179,6 +202,13 @@ class HybridSampler:
             n_in += t.shape[0]
             return c
 
+        def pad_in():
+            """Zero rows up to the next multiple of 8: what follows starts on a 32-byte boundary of the GEMM's float result."""
+            nonlocal n_in
+            if n_in % 8:
+                rows_in.append(torch.zeros(8 - n_in % 8, W, dtype=self._t("embed").dtype, device=self._t("embed").device))
+                n_in += rows_in[-1].shape[0]
+
         def add_out(name):
             nonlocal k_out
             t = self._t(name)
@@ -190,7 +220,7 @@ class HybridSampler:
         for ms in mixer_specs:
             M = _Mixer()
             M.spec, M.cols, M.vec = ms, {}, {}
-            M.k_cache = M.v_cache = M.conv_state = M.state = M.w_lr2 = None
+            M.k_cache = M.v_cache = M.conv_state = M.state = M.w_lr2 = M.w_uk = M.w_uv = None
             q = ms.prefix
             if ms.kind == "window_attention":
                 for n in ("q", "k", "v"):
@@ -232,20 +262,48 @@ class HybridSampler:
                 M.vec["conv"] = torch.cat([self._f(q + n + ".conv") for n in ("q", "k", "v")], 0).contiguous()
                 for n in ("dt_bias", "A_log", "norm"):
                     M.vec[n] = self._f(q + n)
+            elif ms.kind == "latent_attention":
+                for n in ("q", "dkv"):
+                    M.cols[n] = add_in(q + n)
+                if ms.head_gate:
+                    M.cols["g"] = add_in(q + "g")
+                M.vec["dkv.norm"] = self._f(q + "dkv.norm")
+                if ms.head_sink:
+                    M.vec["sink"] = self._f(q + "sink")
+                freq, M.rot_mult = hy.rotary_frequencies(ms.rot_dims, ms.rot_base, ms.rot_scaling)
+                M.vec["freq"] = torch.tensor(freq, dtype=torch.float64, device=dev)
+                # per head: uk [dim, rank] takes a query into the latent space, uv^T [rank, vdim] expands the latent result
+                M.w_uk = self._t(q + "uk").to(device=dev, dtype=wd).reshape(ms.heads, ms.dim, ms.kv_rank).contiguous()
+                M.w_uv = self._t(q + "uv").to(device=dev, dtype=wd).reshape(ms.heads, ms.vdim, ms.kv_rank).transpose(1, 2).contiguous()
+            elif ms.kind == "gla":
+                for n in ("q", "k", "v", "g"):
+                    M.cols[n] = add_in(q + n)
+                M.cols["a1"] = add_in(q + "a1")
+                a2 = self._t(q + "a2")
+                M.rank = a2.shape[1]
+                w2 = torch.zeros(_pad8(a2.shape[0]), _pad8(M.rank), dtype=wd, device=dev)
+                w2[:a2.shape[0], :M.rank] = a2.to(wd)
+                M.w_lr2 = w2
+                M.vec["a2.b"], M.vec["norm"] = self._f(q + "a2.b"), self._f(q + "norm")
             else:
                 raise ValueError(f"unknown mixer kind {ms.kind!r}")
             M.out_col, M.out_size = add_out(q + "o")
             L.mixers.append(M)
         L.ff_col = L.ff_out_col = None
         if with_ff and spec.ff:
-            if spec.ff_kind == "dense":
+            if spec.ff_kind == "dense" and spec.ff_act == "swiglu":      # [gate rows | up rows]
+                c0 = add_in(p + "mlp.gate")[0]
+                add_in(p + "mlp.up")
+                L.ff_col = (c0, 2 * spec.ff)
+                L.ff_out_col = add_out(p + "mlp.down")
+            elif spec.ff_kind == "dense":
                 L.ff_col = add_in(p + "mlp.up")
                 L.ff_out_col = add_out(p + "mlp.down")
             elif spec.ff_kind == "moe" and self._moe_grouped(spec):
                 # sorted-by-expert form: only the router rides in the fused matrix; the experts' matrices are stacked for the
                 # grouped GEMM, [experts * 2 ff, W] (gate rows, then up rows) and [experts * W, ff]
                 L.router_col = add_in(p + "mlp.router")
-                L.router_bias = self._f(p + "mlp.router.b") if self.lm.has_tensor(p + "mlp.router.b") else None
+                L.router_bias = self._router_vector(spec, p)
                 if spec.ff % 32 == 0:                      # gate / up rows interleaved: the SwiGLU is formed in the GEMM's epilogue
                     L.w_gate_up = torch.cat([hy.interleave_gate_up(self._t(f"{p}mlp.e{e}.gate").to(device=dev, dtype=wd),
                                                                    self._t(f"{p}mlp.e{e}.up").to(device=dev, dtype=wd))
@@ -256,7 +314,7 @@ class HybridSampler:
                 L.w_down = torch.cat([self._t(f"{p}mlp.e{e}.down").to(device=dev, dtype=wd) for e in range(spec.experts)], 0).contiguous()
             elif spec.ff_kind == "moe":                   # dense form: router, then per expert its gate rows and its up rows
                 L.router_col = add_in(p + "mlp.router")
-                L.router_bias = self._f(p + "mlp.router.b") if self.lm.has_tensor(p + "mlp.router.b") else None
+                L.router_bias = self._router_vector(spec, p)
                 c0 = n_in
                 for e in range(spec.experts):
                     add_in(f"{p}mlp.e{e}.gate")
@@ -268,6 +326,18 @@ class HybridSampler:
                 L.ff_out_col = (c0, k_out - c0)
             else:
                 raise ValueError(f"unknown feed-forward kind {spec.ff_kind!r}")
+            if spec.ff_kind == "moe" and spec.shared_ff:     # an expert for every token: rides in the fused matrices like a dense one
+                pad_in()
+                c0 = add_in(p + "mlp.shared.gate")[0]
+                add_in(p + "mlp.shared.up")
+                L.shared_col = (c0, 2 * spec.shared_ff)
+                if spec.shared_gate:
+                    L.sg_col = add_in(p + "mlp.shared.sg")
+                L.shared_out_col = add_out(p + "mlp.shared.down")
+        if side:                                          # per-layer token input: gate projection in, projection to the stream out
+            L.side_col = add_in(p + "side.gate")
+            L.side_out_col = add_out(p + "side.proj")
+            L.side_col0 = spec.index * spec.side_dim
         if gate is not None:
             L.gate_col = add_in(gate)
             L.gate_bias = self._f(gate + ".b") if self.lm.has_tensor(gate + ".b") else None
@@ -279,6 +349,11 @@ class HybridSampler:
         if cols_out:
             L.w_out[:, :k_out] = torch.cat([t.to(device=dev, dtype=wd) for t in cols_out], 1)
         return L
+
+    def _router_vector(self, spec, p):
+        """The vector added to the router's outputs before the choice: a bias on the logits, or a correction of the scores."""
+        name = p + ("mlp.correction" if spec.route == "softmax_all" else "mlp.router.b")
+        return self._f(name) if self.lm.has_tensor(name) else None
 
     def _moe_grouped(self, spec) -> bool:
         fits = not self.fp32 and self.cfg.width % 8 == 0 and spec.ff % 8 == 0
@@ -324,6 +399,10 @@ class HybridSampler:
                     M.v_cache = torch.zeros(n, ms.kv_heads, self.PAGE, ms.vdim, dtype=wd, device=dev)
                     ch = ms.heads * ms.dim + ms.kv_heads * (ms.dim + ms.vdim)
                     M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
+                elif ms.kind == "latent_attention":       # one row per token: [normed latent | rotated shared key part]
+                    M.k_cache = torch.zeros(n, 1, self.PAGE, ms.kv_rank + ms.rot_dim, dtype=wd, device=dev)
+                elif ms.kind == "gla":
+                    M.state = torch.zeros(num_slots, ms.heads, ms.dim, ms.vdim, **f32)
                 elif ms.kind == "ssd":
                     ch = ms.heads * ms.vdim + 2 * ms.kv_heads * ms.dim
                     M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
@@ -409,7 +488,116 @@ class HybridSampler:
     def _forward(self, plan: StepPlan, rows: List[int]) -> torch.Tensor:
         if self.stream.kind == "sandwich":
             return self._forward_sandwich(plan, rows)
+        if self.stream.kind == "post_norm":
+            return self._forward_post_norm(plan, rows)
         return self._forward_depth_weighted(plan, rows)
+
+    def _run_mixers(self, L, U, A, plan, eps, ctx=None):
+        for M in L.mixers:
+            out = A[:, M.out_col:M.out_col + M.out_size]
+            kind = M.spec.kind
+            if kind == "latent_attention":
+                self._latent_attention(M, U, plan, eps, out)
+            elif kind == "gla":
+                self._gla(M, U, plan, eps, out)
+            elif kind == "conv_attention":
+                self._conv_attention(M, U, plan, out, ctx, L.spec.index)
+            elif kind == "gated_delta":
+                self._gated_delta(M, U, plan, eps, out)
+            elif kind == "window_attention":
+                self._window_attention(M, U, plan, eps, out)
+            else:
+                self._ssd(M, U, plan, eps, out)
+
+    def _forward_post_norm(self, plan: StepPlan, rows: List[int], keep: Optional[list] = None) -> torch.Tensor:
+        """Stream whose sublayers read x itself: ``x += rmsnorm(sublayer(x)) * w``.  One fused kernel per stage boundary norms the
+        stage's result, adds it and hands the new x to the next stage as GEMM operand (the last one applies the final norm).
+        ``keep``: a list that receives a copy of the stream after every layer."""
+        cfg, dev, wd = self.cfg, self.device, self.wdtype
+        T, W, eps = plan.T, cfg.width, cfg.norm_eps
+        f32 = dict(dtype=torch.float32, device=dev)
+        x = torch.empty(T, W, **f32)
+        h = torch.empty(T, W, dtype=wd, device=dev)
+        hy.embed_norm(self.embed, plan.tokens, self.embed_gain, eps, x, h)
+        ctx: Dict[int, torch.Tensor] = {}
+        for i, L in enumerate(self.layers):
+            U = self._mm(h, L.w_in)                                                   # [T, n_in] float
+            A = (torch.zeros if L.out_pad else torch.empty)(T, L.k_out, dtype=wd, device=dev)
+            self._run_mixers(L, U, A, plan, eps, ctx)
+            self_w = None
+            if L.side_col is not None:
+                (c, n), (oc, on) = L.side_col, L.side_out_col
+                hy.side_gate(U[:, c:c + n], self.side_table, L.side_col0, plan.tokens, A[:, oc:oc + on], n)
+            if L.shared_col is not None:
+                (c, n), (oc, on) = L.shared_col, L.shared_out_col
+                hy.swiglu_cols(U[:, c:c + n], U[:, L.sg_col[0]:L.sg_col[0] + 1] if L.sg_col is not None else None, A[:, oc:oc + on])
+            if L.ff_col is not None:
+                self_w = self._feed_forward(L, U, A)
+            o = self._mm(A, L.w_out) if L.k_out else None                             # [T, W] float
+            if L.w_gate_up is not None:
+                o, self_w = self._experts_grouped(L, U, h, o, want_self=True)
+            last = i + 1 == len(self.layers)
+            hy.post_norm_residual(x, o, self_w, L.w_post, self.final_gain if last else None, eps, h)
+            if keep is not None and (last or self.layers[i + 1].spec.index != L.spec.index):
+                keep.append(x.clone())
+        if not rows:
+            return torch.empty(0, cfg.vocab, **f32)
+        hw = h if rows == list(range(T)) else h[torch.tensor(rows, device=dev)]
+        return self._mm(hw.contiguous(), self.head)[:, :cfg.vocab]
+
+    def _latent_attention(self, M, U, plan, eps, out):
+        """Latent attention in its absorbed form.  The cache holds one row [latent | rotated shared key part] per token; a head's
+        query is taken into that space (``uk_h^T q_unrotated | q_rotated``), the paged kernel treats the row as the one key head
+        whose first ``kv_rank`` columns are also the value, and the latent result is expanded by ``uv_h`` afterwards; the gate and the
+        sink are per head, so they commute with the expansion."""
+        ms = M.spec
+        T, dev, wd = plan.T, U.device, self.wdtype
+        H, dn, dr, r, dv = ms.heads, ms.dim, ms.rot_dim, ms.kv_rank, ms.vdim
+        (cq, nq), (cd, nd) = M.cols["q"], M.cols["dkv"]
+        D = r + dr
+        q = U[:, cq:cq + nq]
+        # queries head-major [H, T, D]: the batched GEMM writes a head's absorbed columns in place, the kernel its rotated ones
+        qa = torch.empty(H, T, D, dtype=torch.float32, device=dev)
+        if self.fp32:
+            qn = q.unflatten(1, (H, dn + dr))[:, :, :dn].transpose(0, 1)                  # a strided view is a valid operand
+            hy.latent_kv_write(q, H, dn, dr, U[:, cd:cd + nd], M.vec["dkv.norm"], eps, M.vec["freq"], ms.rot_dims, M.rot_mult,
+                               ms.rot_layout == "interleaved", plan, M.k_cache, qa)
+            native._count()
+            torch.bmm(qn, M.w_uk, out=qa[:, :, :r])
+        else:
+            qn = torch.empty(H, T, dn, dtype=wd, device=dev)
+            hy.latent_kv_write(q, H, dn, dr, U[:, cd:cd + nd], M.vec["dkv.norm"], eps, M.vec["freq"], ms.rot_dims, M.rot_mult,
+                               ms.rot_layout == "interleaved", plan, M.k_cache, qa, qn)
+            native._count()
+            torch.bmm(qn, M.w_uk, out_dtype=torch.float32, out=qa[:, :, :r])
+        gate = None
+        if ms.head_gate:
+            cg, ng = M.cols["g"]
+            gate = U[:, cg:cg + ng]
+        lat = torch.empty(T, H * r, dtype=wd, device=dev)
+        hy.window_attention(qa, M.k_cache, M.k_cache, plan, 1 << 30, ms.scale, ms.out_scale, lat, gate=gate, head_sink=M.vec.get("sink"),
+                            value_size=r)
+        # expansion per head straight into the out-projection's operand (float32 accumulation, rounded once)
+        native._count()
+        torch.bmm(lat.unflatten(1, (H, r)).transpose(0, 1), M.w_uv, out=out.unflatten(1, (H, dv)).transpose(0, 1))
+
+    def _gla(self, M, U, plan, eps, out):
+        """Gated linear attention: the scan of the delta rule without the delta, decays per key channel from a low-rank projection."""
+        ms = M.spec
+        T, dev = plan.T, U.device
+        nk, nv = ms.heads * ms.dim, ms.heads * ms.vdim
+        cq, _ = M.cols["q"]
+        qkv = U[:, cq:cq + 2 * nk + nv]
+        c1, r = M.cols["a1"]
+        t1 = (torch.zeros if M.w_lr2.shape[1] != r else torch.empty)(T, M.w_lr2.shape[1], dtype=self.wdtype, device=dev)
+        hy.act_cols(U[:, c1:c1 + r], t1[:, :r], "copy")
+        z = self._mm(t1, M.w_lr2)
+        decay = torch.empty(T, nk, dtype=torch.float32, device=dev)
+        hy.gla_prep(qkv, z[:, :nk], M.vec["a2.b"], ms.tau, decay, ms.heads, ms.dim)
+        o = torch.empty(T, nv, dtype=torch.float32, device=dev)
+        hy.delta_scan(qkv, nk, 2 * nk, None, decay, M.state, o, plan, ms.heads, True)
+        cg, ng = M.cols["g"]
+        hy.gated_part_rmsnorm(o, U[:, cg:cg + ng], M.vec["norm"], ms.vdim, "silu", False, eps, ms.out_scale, out)
 
     def _forward_sandwich(self, plan: StepPlan, rows: List[int], keep: Optional[list] = None) -> torch.Tensor:
         """Stream with a norm before and after every sublayer: ``x += norm_b(gate * sublayer(norm(x)))``.  One fused kernel per
@@ -460,30 +648,47 @@ class HybridSampler:
             logits.mul_(st.logit_scale)
         return logits[:, :cfg.vocab]                      # rows keep their padded (16-byte aligned) stride
 
-    def _experts_grouped(self, L, U, h, o):
-        """Route, then run only the chosen experts: rows sorted by expert through two grouped GEMMs."""
+    def _experts_grouped(self, L, U, h, o, want_self: bool = False):
+        """Route, then run only the chosen experts: rows sorted by expert through two grouped GEMMs.  ``want_self``: also return the
+        per-token weight of the chosen identity experts (None without such experts)."""
         spec = L.spec
         T, dev = h.shape[0], h.device
         rc, E = L.router_col
         ids = torch.empty(T, spec.top, dtype=torch.int32, device=dev)
         wts = torch.empty(T, spec.top, dtype=torch.float32, device=dev)
-        hy.moe_route(U[:, rc:rc + E], L.router_bias, spec.top, ids=ids, wts=wts)
+        self_w = None
+        if spec.route == "softmax_all":
+            if spec.identity_experts:
+                self_w = torch.empty(T, dtype=torch.float32, device=dev)
+            hy.moe_route_all(U[:, rc:rc + E], L.router_bias, spec.experts, spec.top, spec.route_scale, ids=ids, wts=wts, self_w=self_w)
+        else:
+            hy.moe_route(U[:, rc:rc + E], L.router_bias, spec.top, ids=ids, wts=wts)
         y = torch.empty(T, self.cfg.width, dtype=torch.float32, device=dev)
-        hy.moe_grouped_ffn(h, ids, wts, L.w_gate_up, L.w_down, E, spec.ff, y, fused_act=spec.ff % 32 == 0)
-        if o is None:
-            return y
-        native._count()
-        return o.add_(y)
+        hy.moe_grouped_ffn(h, ids, wts, L.w_gate_up, L.w_down, spec.experts, spec.ff, y, fused_act=spec.ff % 32 == 0,
+                           identity=spec.identity_experts)
+        if o is not None:
+            native._count()
+            y = o.add_(y)
+        return (y, self_w) if want_self else y
 
     def _feed_forward(self, L, U, A):
         spec = L.spec
         c, n = L.ff_col
         oc, on = L.ff_out_col
+        if spec.ff_kind == "moe" and spec.route == "softmax_all":
+            rc, E = L.router_col
+            self_w = torch.empty(U.shape[0], dtype=torch.float32, device=U.device) if spec.identity_experts else None
+            hy.moe_route_all(U[:, rc:rc + E], L.router_bias, spec.experts, spec.top, spec.route_scale, gu=U[:, c:c + n], ff=spec.ff,
+                             act=A[:, oc:oc + on], self_w=self_w)
+            return self_w
         if spec.ff_kind == "moe":
             rc, E = L.router_col
             hy.moe_route(U[:, rc:rc + E], L.router_bias, spec.top, gu=U[:, c:c + n], ff=spec.ff, act=A[:, oc:oc + on])
+        elif spec.ff_act == "swiglu":
+            hy.swiglu_cols(U[:, c:c + n], None, A[:, oc:oc + on])
         else:
             hy.act_cols(U[:, c:c + n], A[:, oc:oc + on], spec.ff_act)
+        return None
 
     def _conv_attention(self, M, U, plan, out, ctx, layer_index):
         """Biased q / k / v through one short causal convolution (taps carried per slot), values blended with an earlier
