@@ -1,6 +1,7 @@
 """Serving throughput of the hybrid step engine (Nezavik) beside the paged-KV transformer engine (Qwen2) at equal size,
 plus each new kernel against its roofline and against the like kernel of the transformer path; with ``--serve-model vilosun``
-the Vilosun family beside Nezavik (same engine) at equal size, and the kernels it adds beside Nezavik's like kernels.
+the Vilosun family beside Nezavik (same engine) at equal size, and the kernels it adds beside Nezavik's like kernels; with
+``--serve-model damilix`` the Damilix family beside Vilosun in the same way.
 
 Run through ``python bench.py --serve-bench`` (one GPU).  Random weights, synthetic token ids.  End-to-end numbers go
 through the engines' public ``generate`` (two runs that differ by `new` generated tokens: the difference is `new` decode steps,
@@ -236,6 +237,167 @@ def kernels_vilosun(width=2048, batch=16, prompt_len=2048, chunk=1024, decode_ba
     return out
 
 
+def damilix_config(width: int, n_layers: int, vocab: int, experts: int = 16, top: int = 2, kv_rank: int = 256, rot_dim: int = 64):
+    """Heads of 128 (unrotated) + `rot_dim` (rotated) query columns over a latent of `kv_rank` columns, gated linear attention with
+    128 x 128 states, layer pattern latent / gla / gla / latent (second rotation layout); experts as in ``vilosun_config`` plus two
+    identity experts and a shared expert of the same width; a token input of 64 columns per layer."""
+    from nanorlhf_b200.models.damilix import DamilixConfig
+    H = width // 128
+    ff = max(128, (8 * width // (3 * top) + 127) // 128 * 128)
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "identity": 2, "top": top, "scale": 1.5}, "shared": {"ff": ff}}
+    rot = {"base": 1e6, "dims": rot_dim}
+    la = {"type": "latent_attention", "mlp": mlp,
+          "mixer": {"heads": H, "dim": 128, "rot_dim": rot_dim, "vdim": 128, "kv_rank": kv_rank, "scale": (128 + rot_dim) ** -0.5,
+                    "rot": dict(rot, scaling={"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0})}}
+    lb = {"type": "latent_attention_2", "mlp": mlp, "mixer": dict(la["mixer"], rot=rot)}
+    gl = {"type": "gla", "mlp": mlp, "mixer": {"heads": H, "dim": 128, "vdim": 128, "tau": 16.0}}
+    pattern = [la, gl, gl, lb]
+    return DamilixConfig.from_dict({"architecture": "Damilix", "layers": [pattern[i % 4] for i in range(n_layers)], "norm": {"eps": 1e-6},
+                                    "token_side": {"dim": 64}, "vocab": vocab, "width": width})
+
+
+def end_to_end_damilix(width, n_layers, batch, prompt_len, new=128, vocab=32768):
+    """Damilix beside Vilosun (the closest family: same engine, attention + recurrent layers, mixture-of-experts feed-forwards) at
+    equal width, depth and expert sizes."""
+    from nanorlhf_b200.models.damilix import DamilixForCausalLM
+    from nanorlhf_b200.models.vilosun import VilosunForCausalLM
+    from nanorlhf_b200.sampler.hybrid_sampler import HybridSampler
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, vocab - 2, (batch, prompt_len), generator=g).tolist()
+    res = {"width": width, "layers": n_layers, "batch": batch, "prompt_len": prompt_len, "new_tokens": new}
+    for name, make in (("damilix", lambda: DamilixForCausalLM.from_config(damilix_config(width, n_layers, vocab), torch.bfloat16, dev, seed=0, gla_rank=64)),
+                       ("vilosun", lambda: VilosunForCausalLM.from_config(vilosun_config(width, n_layers, vocab), torch.bfloat16, dev, seed=0))):
+        model = make()
+        eng = HybridSampler(model, dtype="bf16", max_num_seqs=batch, prefill_token_budget=16384)
+        pre, step = _gen_times(lambda p, mt: eng.generate(p, 1, 1.0, 1.0, mt, None, vocab - 1, 1), prompts, new)
+        res[name] = {"params_m": round(sum(p.numel() for p in model.parameters()) / 1e6, 1),
+                     "prefill_tok_s": round(batch * prompt_len / pre), "decode_tok_s": round(batch / step),
+                     "decode_ms_per_step": round(step * 1e3, 3)}
+        eng.release()
+        del eng, model
+        torch.cuda.empty_cache()
+    return res
+
+
+def kernels_damilix(width=2048, batch=16, prompt_len=2048, decode_batch=256, ctx=2048, experts=16, top=2, kv_rank=256, rot_dim=64):
+    """The kernels Damilix adds to the step engine, each beside the like kernel of the Vilosun path."""
+    from nanorlhf_b200 import _C
+    from nanorlhf_b200.ops import hybrid as hy
+    from nanorlhf_b200.sampler.hybrid_sampler import StepPlan
+    hbm, flops_peak, which = _peaks()
+    dev = torch.device("cuda:0")
+    out = {"roofline": which, "width": width}
+    H, Hkv, D = width // 128, max(1, width // 512), 128
+    DL = kv_rank + rot_dim
+    ff = max(128, (8 * width // (3 * top) + 127) // 128 * 128)
+
+    def plan_for(B, n_new, n_old):
+        s = _C.StepScheduler((n_old + n_new + 15) // 16 * B + 8, 16, B)
+        sids = [s.open() for _ in range(B)]
+        if n_old:
+            s.plan(sids, [n_old] * B)
+        data, E, T, MB = s.plan(sids, [n_new] * B)
+        return StepPlan(torch.from_numpy(data).to(dev), E, T, MB), s
+
+    def report(name, sec, bytes_, flops=0.0):
+        floor = max(bytes_ / hbm, flops / flops_peak)
+        out[name] = {"us": round(sec * 1e6, 1), "gb_s": round(bytes_ / sec / 1e9, 1), "tflop_s": round(flops / sec / 1e12, 2),
+                     "roofline_frac": round(floor / sec, 3)}
+
+    for phase, B, n_new, n_old in (("prefill", batch, prompt_len, 0), ("decode", decode_batch, 1, ctx - 1)):
+        plan, sched = plan_for(B, n_new, n_old)
+        T = plan.T
+        f32 = dict(dtype=torch.float32, device=dev)
+        plan.tokens.copy_(torch.randint(0, 32000, (T,), dtype=torch.int32, device=dev))
+        # -- embedding: normed rows vs scaled rows + hashed pair rows
+        emb, pair = torch.randn(32768, width, device=dev).bfloat16(), torch.randn(65522, width, device=dev).bfloat16()
+        x0, h = torch.empty(T, width, **f32), torch.empty(T, width, dtype=torch.bfloat16, device=dev)
+        wa, wb = torch.ones(width, **f32), torch.ones(width, **f32)
+        sec = _time(lambda: hy.embed_norm(emb, plan.tokens, wa, 1e-6, x0, h))
+        report(f"{phase}.embed_norm", sec, T * width * 8.0)
+        prev = torch.zeros(B, dtype=torch.int32, device=dev)
+        sec = _time(lambda: hy.embed_hashed(emb, pair, plan, prev, 1.0, 48271, 16807, 65521, x0))
+        report(f"{phase}.vilosun.embed_hashed", sec, T * width * 8.0)
+        # -- sublayer boundary: norm of the result + residual add + operand cast vs gate, post-norm, residual, pre-norm
+        x, o, gate = torch.randn(T, width, **f32), torch.randn(T, width, **f32), torch.randn(T, width, **f32)
+        sw, gb = torch.rand(T, **f32), torch.randn(width, **f32)
+        sec = _time(lambda: hy.post_norm_residual(x, o, sw, wa, None, 1e-6, h))
+        report(f"{phase}.post_norm_residual", sec, T * width * (4.0 * 3 + 2))
+        sec = _time(lambda: hy.group_norm_residual(x, o, gate, gb, wa, wb, 2, 1e-6, h))
+        report(f"{phase}.vilosun.group_norm_residual", sec, T * width * (4.0 * 4 + 2))
+        # -- token input gate and the shared expert's gated SwiGLU vs the squared-ReLU activation
+        u = torch.randn(T, 64, **f32)
+        table = torch.randn(32768, 8 * 64, device=dev).bfloat16()
+        sg_out = torch.empty(T, 64, dtype=torch.bfloat16, device=dev)
+        sec = _time(lambda: hy.side_gate(u, table, 128, plan.tokens, sg_out, 64))
+        report(f"{phase}.side_gate", sec, T * 64 * (4.0 + 2 + 2))
+        gu, rg = torch.randn(T, 2 * ff, **f32), torch.randn(T, 1, **f32)
+        act = torch.empty(T, ff, dtype=torch.bfloat16, device=dev)
+        sec = _time(lambda: hy.swiglu_cols(gu, rg, act))
+        report(f"{phase}.swiglu_cols(row gate)", sec, T * ff * (8.0 + 2))
+        up, ub = torch.randn(T, 2 * ff, **f32), torch.empty(T, 2 * ff, dtype=torch.bfloat16, device=dev)
+        sec = _time(lambda: hy.act_cols(up, ub, "relu2"))
+        report(f"{phase}.nezavik.relu2", sec, T * 2 * ff * 6.0)
+        del gu, up, ub, act
+        # -- routing
+        zr, corr = torch.randn(T, experts + 2, **f32), torch.randn(experts + 2, **f32) * 0.01
+        ids, wts, selfw = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, **f32), torch.empty(T, **f32)
+        sec = _time(lambda: hy.moe_route_all(zr, corr, experts, top, 1.5, ids=ids, wts=wts, self_w=selfw))
+        report(f"{phase}.moe_route_all(ids and weights)", sec, T * ((experts + 2) * 4.0 + top * 8.0 + 4.0))
+        sec = _time(lambda: hy.moe_route(zr[:, :experts], corr[:experts], top, ids=ids, wts=wts))
+        report(f"{phase}.vilosun.moe_route(ids and weights)", sec, T * (experts * 4.0 + top * 8.0))
+        # -- latent attention: cache write + rotation, attention over the latent rows vs page write, chunk attention
+        q = torch.randn(T, H * (128 + rot_dim), **f32)
+        dkv, nw = torch.randn(T, DL, **f32), torch.ones(kv_rank, **f32)
+        fr, mult = hy.rotary_frequencies(rot_dim, 1e6, {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+        freq = torch.tensor(fr, dtype=torch.float64, device=dev)
+        n_pages = sched.num_free_blocks() + plan.max_blocks * B + 8
+        lc = torch.randn(n_pages, 1, 16, DL, device=dev).bfloat16()
+        qa = torch.randn(T, H * DL, **f32)
+        sec = _time(lambda: hy.latent_kv_write(q, H, 128, rot_dim, dkv, nw, 1e-6, freq, rot_dim, mult, True, plan, lc, qa))
+        report(f"{phase}.latent_kv_write", sec, T * (DL * 4.0 + DL * 2.0 + H * rot_dim * 8.0))
+        nq, nk = H * D, Hkv * D
+        kc = torch.randn(n_pages, Hkv, 16, D, device=dev).bfloat16()
+        vc = torch.randn_like(kc)
+        k_, v_, vo, lam = torch.randn(T, nk, **f32), torch.randn(T, nk, **f32), torch.randn(T, nk, **f32), torch.full((1,), 0.3, **f32)
+        sec = _time(lambda: hy.kv_write_blend(k_, v_, vo, lam, kc, vc, plan))
+        report(f"{phase}.vilosun.kv_write_blend", sec, T * nk * (4.0 * 4 + 2 * 2))
+        sink, hg = torch.randn(H, **f32), torch.randn(T, H, **f32)
+        lat = torch.empty(T, H * kv_rank, dtype=torch.bfloat16, device=dev)
+        keys = (sum(p + 1 for p in range(n_new)) if phase == "prefill" else ctx) * B
+        byt = (T * H * DL * 4.0 + T * H * kv_rank * 2.0 + T * DL * 2.0) if phase == "prefill" else (keys * DL * 2.0 + T * H * (DL * 4.0 + kv_rank * 2.0))
+        sec = _time(lambda: hy.window_attention(qa, lc, lc, plan, 1 << 30, 0.07, 1.0, lat, gate=hg, head_sink=sink, value_size=kv_rank), iters=3, warm=1)
+        report(f"{phase}.latent_attention(row {DL}, value {kv_rank})", sec, byt, flops=2.0 * keys * H * (DL + kv_rank))
+        qv = torch.randn(T, nq, **f32)
+        ao = torch.empty(T, nq, dtype=torch.bfloat16, device=dev)
+        temp, slope = torch.rand(H, **f32) + 0.5, torch.rand(H, **f32) * 0.1
+        chunk = 1024
+        keys_c = (sum(p % chunk + 1 for p in range(n_new)) if phase == "prefill" else ((ctx - 1) % chunk + 1)) * B
+        byt_c = (T * H * D * 6.0 + T * 2 * Hkv * D * 2.0) if phase == "prefill" else (keys_c * 2 * Hkv * D * 2.0 + T * H * D * 6.0)
+        sec = _time(lambda: hy.window_attention(qv, kc, vc, plan, chunk, D ** -0.5, 1.0, ao, chunked=True, head_scale=temp,
+                                                head_slope=slope, gate=hg), iters=3, warm=1)
+        report(f"{phase}.vilosun.chunk_attention(c={chunk})", sec, byt_c, flops=4.0 * keys_c * H * D)
+        del kc, vc, lc, qa, lat
+        # -- gated linear attention vs the gated delta rule (same state size)
+        nkk = H * D
+        qkv = torch.randn(T, 3 * nkk, **f32) * 0.1
+        z, ab = torch.randn(T, nkk, **f32), torch.full((nkk,), 3.0, **f32)
+        decay, og = torch.empty(T, nkk, **f32), torch.empty(T, nkk, **f32)
+        state = torch.zeros(B, H, D, D, **f32)
+        sec = _time(lambda: hy.gla_prep(qkv, z, ab, 16.0, decay, H, D))
+        report(f"{phase}.gla_prep", sec, T * nkk * 16.0)
+        sec = _time(lambda: hy.delta_scan(qkv, nkk, 2 * nkk, None, decay, state, og, plan, H, True), iters=3, warm=1)
+        sbytes = B * H * D * D * 8.0 + T * nkk * 20.0
+        report(f"{phase}.gla_scan", sec, sbytes, flops=0.0)
+        out[f"{phase}.gla_scan"]["fp32_fma_frac"] = round(4.0 * T * H * D * D / sec / 72e12, 3)
+        beta = torch.rand(T, H, **f32)
+        sec = _time(lambda: hy.delta_scan(qkv, nkk, 2 * nkk, beta, decay, state, og, plan, H, True), iters=3, warm=1)
+        report(f"{phase}.vilosun.delta_scan(per channel)", sec, sbytes)
+        out[f"{phase}.vilosun.delta_scan(per channel)"]["fp32_fma_frac"] = round(6.0 * T * H * D * D / sec / 72e12, 3)
+    return out
+
+
 def end_to_end(width, n_layers, batch, prompt_len, new=128, vocab=32768):
     from nanorlhf_b200.models.nezavik import NezavikForCausalLM
     from nanorlhf_b200.models.qwen2 import Qwen2Config, Qwen2ForCausalLM
@@ -387,6 +549,18 @@ def main(quick: bool = False, small: bool = False, model: str = "nezavik"):
     from nanorlhf_b200.ops import native
     global SMALL
     native.load()
+    if model == "damilix":
+        SMALL = small
+        if small:
+            print(json.dumps({"bench": "serve-damilix-small",
+                              "kernels": kernels_damilix(width=1024, batch=8, prompt_len=1024, decode_batch=64, ctx=1024)}))
+            return None
+        res = {"bench": "serve-damilix", "kernels": kernels_damilix(), "end_to_end": []}
+        for width, layers, batch, plen in ((1024, 8, 32, 1024), (2048, 8, 16, 2048)) if not quick else ((1024, 4, 8, 512),):
+            res["end_to_end"].append(end_to_end_damilix(width, layers, batch, plen))
+        res["gpu_launches"] = native.launches()
+        print(json.dumps(res))
+        return res
     if model == "vilosun":
         SMALL = small
         if small:
@@ -412,4 +586,5 @@ def main(quick: bool = False, small: bool = False, model: str = "nezavik"):
 
 
 if __name__ == "__main__":
-    main(quick="--quick" in sys.argv, small="--small" in sys.argv, model="vilosun" if "--vilosun" in sys.argv else "nezavik")
+    main(quick="--quick" in sys.argv, small="--small" in sys.argv,
+         model="damilix" if "--damilix" in sys.argv else "vilosun" if "--vilosun" in sys.argv else "nezavik")
