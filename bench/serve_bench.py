@@ -367,7 +367,8 @@ def kernels_damilix(width=2048, batch=16, prompt_len=2048, decode_batch=256, ctx
         lat = torch.empty(T, H * kv_rank, dtype=torch.bfloat16, device=dev)
         keys = (sum(p + 1 for p in range(n_new)) if phase == "prefill" else ctx) * B
         byt = (T * H * DL * 4.0 + T * H * kv_rank * 2.0 + T * DL * 2.0) if phase == "prefill" else (keys * DL * 2.0 + T * H * (DL * 4.0 + kv_rank * 2.0))
-        sec = _time(lambda: hy.window_attention(qa, lc, lc, plan, 1 << 30, 0.07, 1.0, lat, gate=hg, head_sink=sink, value_size=kv_rank), iters=3, warm=1)
+        it, wm = (3, 1) if phase == "prefill" else (20, 5)
+        sec = _time(lambda: hy.window_attention(qa, lc, lc, plan, 1 << 30, 0.07, 1.0, lat, gate=hg, head_sink=sink, value_size=kv_rank), iters=it, warm=wm)
         report(f"{phase}.latent_attention(row {DL}, value {kv_rank})", sec, byt, flops=2.0 * keys * H * (DL + kv_rank))
         qv = torch.randn(T, nq, **f32)
         ao = torch.empty(T, nq, dtype=torch.bfloat16, device=dev)
@@ -376,7 +377,7 @@ def kernels_damilix(width=2048, batch=16, prompt_len=2048, decode_batch=256, ctx
         keys_c = (sum(p % chunk + 1 for p in range(n_new)) if phase == "prefill" else ((ctx - 1) % chunk + 1)) * B
         byt_c = (T * H * D * 6.0 + T * 2 * Hkv * D * 2.0) if phase == "prefill" else (keys_c * 2 * Hkv * D * 2.0 + T * H * D * 6.0)
         sec = _time(lambda: hy.window_attention(qv, kc, vc, plan, chunk, D ** -0.5, 1.0, ao, chunked=True, head_scale=temp,
-                                                head_slope=slope, gate=hg), iters=3, warm=1)
+                                                head_slope=slope, gate=hg), iters=it, warm=wm)
         report(f"{phase}.vilosun.chunk_attention(c={chunk})", sec, byt_c, flops=4.0 * keys_c * H * D)
         del kc, vc, lc, qa, lat
         # -- gated linear attention vs the gated delta rule (same state size)

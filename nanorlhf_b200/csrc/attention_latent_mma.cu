@@ -6,8 +6,8 @@
 // Prompt portions (latent_attention_mma_kernel): a block owns 64 query rows -- QT consecutive tokens x HB heads -- as four
 // warps of 16 rows and walks the keys its rows can see in blocks of 64 or 32 (whole pages), double buffered with cp.async.
 // Rows can be up to 576 columns wide (tiles of 128 to 576 columns), so the queries stay in shared memory (A fragments are
-// fetched per 16 columns) and a block accumulates a slice of 128 value columns; further slices are further blocks (they
-// repeat S, which costs D / Dv of their P V).
+// fetched per 16 columns) and a block accumulates a slice of 128 or (values wider than 128) 256 value columns; further slices
+// are further blocks, which repeat S.
 // Scores, mask and online softmax are float (base 2, ex2.approx); P is rounded to bf16 only as the operand of O += P V.
 // Steps of single tokens (latent_attention_decode_kernel): every warp walks its own pages for up to 16 heads and leaves
 // (O, max, l) as one part; window_attention_merge (attention_window_mma.cu's form, here with the sink) combines the parts.
@@ -23,7 +23,6 @@ namespace {
 constexpr int kBM = 64;        // query rows per block
 constexpr int kThreads = 128;
 constexpr int kPad = 8;        // bf16 elements appended to a shared-memory row (ldmatrix without bank conflicts)
-constexpr int kVS = 128;       // value columns per block
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -79,27 +78,31 @@ __device__ __forceinline__ void load_rows(__nv_bfloat16* dst, const __nv_bfloat1
   }
 }
 
-// shared memory of the prompt kernel: two key buffers and the queries; two blocks per SM need <= 113 KB each
-__host__ __device__ constexpr size_t prefill_smem(int ks, int bn) { return sizeof(__nv_bfloat16) * (2 * bn + kBM) * (16 * ks + kPad); }
+// shared memory of the prompt kernel: ST key buffers and the queries; two blocks per SM need <= 113 KB each, three <= 75 KB
+__host__ __device__ constexpr size_t prefill_smem(int ks, int bn, int st) {
+  return sizeof(__nv_bfloat16) * (st * bn + kBM) * (16 * ks + kPad);
+}
 
-template <int KS, int BN>      // padded D = 16 KS; BN keys per block of the walk (64, or 32 where that lets two blocks share an SM)
-__global__ void __launch_bounds__(kThreads, prefill_smem(KS, BN) <= 75 * 1024 ? 3 : prefill_smem(KS, BN) <= 113 * 1024 ? 2 : 1)
+// padded D = 16 KS; BN keys per block of the walk (64, or 32 where that lets two blocks share an SM); ST key buffers in flight;
+// VG 16-column value groups per block (8, or 16: all of 256 value columns from one S, at 128 accumulator registers)
+template <int KS, int BN, int ST, int VG>
+__global__ void __launch_bounds__(kThreads, (VG <= 8 && prefill_smem(KS, BN, ST) <= 75 * 1024) ? 3 : prefill_smem(KS, BN, ST) <= 113 * 1024 ? 2 : 1)
 latent_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfloat16* __restrict__ cache,
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_entry,
                             const int* __restrict__ pos, float scale, float out_scale, __nv_bfloat16* __restrict__ out, long so, int T,
                             int H, int D, int Dv, int HB, int QT, NrlAttnMods md) {
   constexpr int DP = 16 * KS, LDK = DP + kPad;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [2][BN][LDK]
-  __nv_bfloat16* sQ = sK + 2 * BN * LDK;                                      // [kBM][LDK]
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [ST][BN][LDK]
+  __nv_bfloat16* sQ = sK + ST * BN * LDK;                                     // [kBM][LDK]
   constexpr int NB = BN / 8;                                                  // 8-key score fragments per block
   const int zb = static_cast<int>(blockIdx.z), vs = static_cast<int>(blockIdx.y);
   const int h0 = zb * HB, hb = min(HB, H - zb * HB);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
   const int t_begin = blockIdx.x * QT, t_end = min(T, t_begin + QT);
   const long qhs = md.q_head_stride ? md.q_head_stride : D;
-  const int v0 = vs * kVS;                                  // first value column of this block
-  const int nvg = min(8, (DP - v0) / 16);                   // 16-column groups of the slice that lie inside the tile
+  const int v0 = vs * VG * 16;                              // first value column of this block
+  const int nvg = min(VG, (DP - v0) / 16);                   // 16-column groups of the slice that lie inside the tile
 
   for (int idx = threadIdx.x; idx < kBM * DP; idx += kThreads) {
     const int r = idx / DP, c = idx - r * DP;
@@ -120,9 +123,9 @@ latent_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
   const int wt_lo = t_begin + (w * 16) / HB, wt_hi = min(t_end - 1, t_begin + (w * 16 + 15) / HB);
   const uint32_t q_addr = smem_u32(sQ + (w * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDK + (lane >> 4) * 8);
 
-  float o[16][4];
+  float o[2 * VG][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < 2 * VG; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // running maxima live in the log2 domain
   const float sl2 = scale * kLog2e;
 
@@ -150,19 +153,22 @@ latent_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     __syncthreads();                                       // the previous run's last block has been consumed
     int pg[4];
     block_pages(bt, 0, hi, pg);
-    load_rows<DP, BN>(sK, cache, pg, 0, hi, D);
-    cp_commit();
-    if (nblk > 1) block_pages(bt, BN, hi, pg);
-    for (int ib = 0; ib < nblk; ++ib) {
-      const int kb = ib * BN, buf = ib & 1;
-      if (ib + 1 < nblk) {
-        load_rows<DP, BN>(sK + (buf ^ 1) * BN * LDK, cache, pg, kb + BN, hi, D);
-        cp_commit();
-        if (ib + 2 < nblk) block_pages(bt, kb + 2 * BN, hi, pg);
-        cp_wait<1>();
-      } else {
-        cp_wait<0>();
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) {                      // ST - 1 key blocks in flight before the first is used
+      if (i < nblk) {
+        load_rows<DP, BN>(sK + i * BN * LDK, cache, pg, i * BN, hi, D);
+        if (i + 1 < nblk) block_pages(bt, (i + 1) * BN, hi, pg);      // page ids are fetched a block ahead of their use
       }
+      cp_commit();                                         // (an empty group keeps the count per iteration fixed)
+    }
+    for (int ib = 0; ib < nblk; ++ib) {
+      const int kb = ib * BN, buf = ib % ST, nxt = ib + ST - 1;
+      if (nxt < nblk) {                                    // its buffer held block ib - 1, which every warp has left
+        load_rows<DP, BN>(sK + (nxt % ST) * BN * LDK, cache, pg, nxt * BN, hi, D);
+        if (nxt + 1 < nblk) block_pages(bt, (nxt + 1) * BN, hi, pg);
+      }
+      cp_commit();
+      cp_wait<ST - 1>();
       __syncthreads();
       if (warp_in && kb <= whi) {
         const __nv_bfloat16* bK = sK + buf * BN * LDK;
@@ -230,7 +236,7 @@ latent_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
           }
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 2 * VG; ++i) {
           o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
         }
         {
@@ -244,7 +250,7 @@ latent_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
             pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
             pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-            for (int nv = 0; nv < 8; ++nv) {
+            for (int nv = 0; nv < VG; ++nv) {
               if (nv < nvg) {
                 uint32_t b[4];
                 ldsm_x4_t(v_addr + (kk * 16 * LDK + nv * 16) * 2, b);
@@ -272,7 +278,7 @@ latent_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     float f = out_scale / l;
     if (md.gate != nullptr) f *= sigmoid_(md.gate[static_cast<long>(row_t[hf]) * md.gate_stride + hq]);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 2 * VG; ++i) {
       const int c = v0 + i * 8 + 2 * tq;
       if (c < Dv) *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(o[i][2 * hf] * f, o[i][2 * hf + 1] * f);
     }
@@ -315,15 +321,32 @@ latent_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
   const int per_part = (npages + nparts - 1) / nparts;
   const int pg0 = pi * per_part, pg1 = min(npages, pg0 + per_part);          // this warp's pages [pg0, pg1)
 
+  // A page is 16 rows of D columns, contiguous in global memory; in shared memory its rows are LDK apart.  The padding columns
+  // (D .. DP) of every stage are zeroed once; a page's copy then walks the real 16-byte chunks with running (row, chunk) counters.
+  const int dch = D >> 3;                                  // real 16-byte chunks per row
+  if (dch < DP / 8) {
+    for (int idx = lane; idx < STAGES * 16 * (DP / 8 - dch); idx += 32) {
+      const int row = idx / (DP / 8 - dch), ch = dch + idx % (DP / 8 - dch);
+      *reinterpret_cast<uint4*>(ring + row * LDK + ch * 8) = make_uint4(0u, 0u, 0u, 0u);      // rows of all stages are LDK apart
+    }
+  }
+  const int key_first = lane / dch, ch_first = lane - key_first * dch;
+  const int key_step = 32 / dch, ch_step = 32 - key_step * dch;
   auto load_page = [&](int stage, int pg) {
     __nv_bfloat16* sK = ring + stage * kStageElems;
-    const long cell0 = static_cast<long>(bt[pg]) * 16;
-    constexpr int kch = DP / 8;
-    for (int idx = lane; idx < 16 * kch; idx += 32) {
-      const int key = idx / kch, ch = idx - key * kch;
+    const __nv_bfloat16* src = cache + static_cast<long>(bt[pg]) * 16 * D;
+    const int last = min(15, p - pg * 16);                 // rows after the token's own (last page only) are zero-filled
+    int key = key_first, ch = ch_first;
+    for (int idx = lane; idx < 16 * dch; idx += 32) {
       __nv_bfloat16* d = sK + key * LDK + ch * 8;
-      if (pg * 16 + key <= p && ch * 8 < D) cp_async16(smem_u32(d), cache + (cell0 + key) * D + ch * 8);
-      else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);          // padding, or cells after the token
+      if (key <= last) cp_async16(smem_u32(d), src + static_cast<long>(idx) * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+      key += key_step;
+      ch += ch_step;
+      if (ch >= dch) {
+        ch -= dch;
+        ++key;
+      }
     }
   };
 
@@ -348,13 +371,31 @@ latent_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
     {
       const int m = lane >> 3;
       const uint32_t k_addr = smem_u32(bK + ((m >> 1) * 8 + (lane & 7)) * LDK + (m & 1) * 8);
-#pragma unroll 4
-      for (int ks = 0; ks < KS; ++ks) {
-        uint32_t qf[4], b[4];
+      // two accumulator sets (even / odd 16-column steps): the chain of dependent mma is half as long
+      float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 2
+      for (int ks = 0; ks + 1 < KS; ks += 2) {
+        uint32_t qf[4], b[4], qg[4], c[4];
         ldsm_x4(q_addr + ks * 32, qf);
         ldsm_x4(k_addr + ks * 32, b);
+        ldsm_x4(q_addr + ks * 32 + 32, qg);
+        ldsm_x4(k_addr + ks * 32 + 32, c);
         mma_bf16(s[0], qf, b[0], b[1]);
         mma_bf16(s[1], qf, b[2], b[3]);
+        mma_bf16(s2[0], qg, c[0], c[1]);
+        mma_bf16(s2[1], qg, c[2], c[3]);
+      }
+      if (KS & 1) {
+        uint32_t qf[4], b[4];
+        ldsm_x4(q_addr + (KS - 1) * 32, qf);
+        ldsm_x4(k_addr + (KS - 1) * 32, b);
+        mma_bf16(s[0], qf, b[0], b[1]);
+        mma_bf16(s[1], qf, b[2], b[3]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s[0][i] += s2[0][i];
+        s[1][i] += s2[1][i];
       }
     }
     float mrow[2] = {-INFINITY, -INFINITY};
@@ -388,9 +429,11 @@ latent_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
         l_run[i >> 1] += pr;
       }
     }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {      // a maximum grew (rare after the first pages)
 #pragma unroll
-    for (int i = 0; i < 2 * VG; ++i) {
-      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      for (int i = 0; i < 2 * VG; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
     }
     {
       uint32_t pa[4];
@@ -470,20 +513,20 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part, in
   }
 }
 
-template <int KS, int BN>
+template <int KS, int BN, int ST, int VG>
 cudaError_t launch_prefill(const float* q, long sq, const void* cache, const int* block_table, int max_blocks, const int* tok_entry,
                            const int* pos, float scale, float out_scale, void* out, long so, int T, int H, int D, int Dv, int single_token,
                            const NrlAttnMods& md, cudaStream_t s) {
   const int HB = H < kBM ? H : kBM, QT = single_token ? 1 : kBM / HB;
-  constexpr size_t smem = prefill_smem(KS, BN);
-  auto kern = latent_attention_mma_kernel<KS, BN>;
+  constexpr size_t smem = prefill_smem(KS, BN, ST);
+  auto kern = latent_attention_mma_kernel<KS, BN, ST, VG>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const dim3 grid((T + QT - 1) / QT, (Dv + kVS - 1) / kVS, (H + HB - 1) / HB);
+  const dim3 grid((T + QT - 1) / QT, (Dv + VG * 16 - 1) / (VG * 16), (H + HB - 1) / HB);
   kern<<<grid, kThreads, smem, s>>>(q, sq, static_cast<const __nv_bfloat16*>(cache), block_table, max_blocks, tok_entry, pos, scale,
                                     out_scale, static_cast<__nv_bfloat16*>(out), so, T, H, D, Dv, HB, QT, md);
   return cudaGetLastError();
@@ -550,15 +593,22 @@ cudaError_t nrl_latent_attention_mma(const float* q, long sq, const void* cache,
   if (ks == KS_)                                                                                                                 \
     return launch_decode<KS_, ST_, VG_>(q, sq, cache, block_table, max_blocks, tok_entry, pos, scale, out_scale, out, so, T, H, D, Dv,  \
                                         nsplit, part, md, s);
-    NRL_LD(8, 3, 8) NRL_LD(12, 3, 16) NRL_LD(16, 3, 16) NRL_LD(20, 2, 16) NRL_LD(24, 2, 16) NRL_LD(28, 2, 16) NRL_LD(36, 2, 16)
+    // stages: two blocks per SM where shared memory allows (rows up to 384 columns) -- at rows of 320 columns one block with a
+    // five-page ring per warp measured 163 us where two blocks with two pages each take 120: the warps' instruction streams,
+    // not the bytes in flight, bound the walk
+    NRL_LD(8, 3, 8) NRL_LD(12, 4, 16) NRL_LD(16, 3, 16) NRL_LD(20, 2, 16) NRL_LD(24, 2, 16) NRL_LD(28, 3, 16) NRL_LD(36, 2, 16)
 #undef NRL_LD
   }
-#define NRL_LP(KS_, BN_)                                                                                                         \
+#define NRL_LP(KS_, BN_, ST_)                                                                                                    \
+  if (ks == KS_ && (KS_ <= 8 || Dv <= 128))                                                                                      \
+    return launch_prefill<KS_, BN_, ST_, 8>(q, sq, cache, block_table, max_blocks, tok_entry, pos, scale, out_scale, out, so, T, H, \
+                                            D, Dv, single_token, md, s);                                                          \
   if (ks == KS_)                                                                                                                 \
-    return launch_prefill<KS_, BN_>(q, sq, cache, block_table, max_blocks, tok_entry, pos, scale, out_scale, out, so, T, H, D, Dv,  \
-                                    single_token, md, s);
-  // 64 keys per block where two or three blocks still share an SM, else 32 (two blocks up to rows of 384 columns)
-  NRL_LP(8, 64) NRL_LP(12, 64) NRL_LP(16, 32) NRL_LP(20, 32) NRL_LP(24, 32) NRL_LP(28, 32) NRL_LP(36, 32)
+    return launch_prefill<(KS_ <= 8 ? 12 : KS_), BN_, ST_, 16>(q, sq, cache, block_table, max_blocks, tok_entry, pos, scale, out_scale, \
+                                                               out, so, T, H, D, Dv, single_token, md, s);
+  // 64 keys per block where two or three blocks still share an SM, else 32 (two blocks up to rows of 384 columns); a third
+  // key buffer where it costs no block per SM
+  NRL_LP(8, 64, 2) NRL_LP(12, 64, 2) NRL_LP(16, 32, 2) NRL_LP(20, 32, 3) NRL_LP(24, 32, 2) NRL_LP(28, 32, 3) NRL_LP(36, 32, 3)
 #undef NRL_LP
   return cudaErrorInvalidValue;
 }

@@ -308,6 +308,20 @@ def test_latent_attention_on_the_tensor_cores(tmp_path, sizes):
         assert (got - want).pow(2).mean().sqrt() < 6e-3 * scale, cuts[:4]
 
 
+def test_latent_attention_long_context_on_the_tensor_cores(tmp_path):
+    """Hundreds of keys per query: many key blocks per tile, portions that start and end inside pages and key blocks, single-token
+    steps whose page walk is cut into parts."""
+    T = 700
+    needles = [(690, 5), (650, 330), (331, 332), (420, 419), (699, 699)]
+    run, want = _latent_case(tmp_path, "half", "bf16", T, needles, heads=4, dim=16, rot_dim=24, vdim=16, kv_rank=280, scale=0.2, base=1000.0,
+                             scaling=None)
+    scale = want.abs().max()
+    for cuts in ([T], [100, 1, 250, 3, 346], [650] + [1] * 50):
+        got = run(cuts)
+        assert (got - want).abs().max() < 4e-2 * scale, cuts[:4]
+        assert (got - want).pow(2).mean().sqrt() < 6e-3 * scale, cuts[:4]
+
+
 def test_latent_attention_batches_on_the_tensor_cores(tmp_path):
     """Several sequences of unequal lengths in one step (tiles that span sequences) and single-token steps of a batch, bf16."""
     cfg = O.make_config(layers=("latent",), ffs=(None,), side=0, latent=dict(heads=7, dim=24, rot_dim=24, vdim=40, kv_rank=112, scale=0.2, scaling=None))
