@@ -623,3 +623,22 @@ def test_trace_runner_replays_a_mixed_trace(tmp_path):
     for i, rows in want.items():
         got = torch.from_numpy(np.fromfile(os.path.join(outdir, f"{i}.f32"), dtype="<f4").reshape(len(rows), cfg["vocab"])).double()
         assert _rel(got, torch.stack(rows)) < F32_TOL
+
+
+def test_sampler_command_line_generates_greedily(tmp_path):
+    """``python -m nanorlhf_b200.sampler`` on a Damilix checkpoint: the class and the engine come from config.json."""
+    cfg, W = _model("plain")
+    path = _save(tmp_path, cfg, W)
+    prompts = [_tokens(cfg, 7, 1), _tokens(cfg, 19, 2)]
+    cmd = [sys.executable, "-m", "nanorlhf_b200.sampler", "--model", path, "--dtype", "float32", "--max-tokens", "6"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(map(str, p))]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = [json.loads(ln) for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert [(x["prompt"], x["sample"]) for x in rows] == [(0, 0), (1, 0)]
+    for p, x in zip(prompts, rows):
+        seq = list(p)
+        for t in x["tokens"]:
+            assert t == int(O.forward(W, cfg, seq)[-1].argmax())
+            seq.append(t)
