@@ -1,5 +1,6 @@
 """Op layer of hybrid (attention + recurrent-state) decoders: thin, launch-counting wrappers over the sm_100a kernels of
-``csrc/stream_ops.cu``, ``csrc/recurrent.cu``, ``csrc/attention_window.cu`` / ``attention_window_mma.cu`` and ``csrc/moe.cu``
+``csrc/stream_ops.cu``, ``csrc/recurrent.cu``, ``csrc/attention_window.cu`` / ``attention_window_mma.cu`` /
+``attention_latent_mma.cu`` and ``csrc/moe.cu``
 (with the grouped form of ``csrc/gemm_tc.cu``).
 
 All of them take the step plan of ``_C.StepScheduler.plan`` (entries = runs of consecutive tokens of one sequence) and

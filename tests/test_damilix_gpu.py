@@ -101,6 +101,9 @@ SHAPES = {
                                scaling=dict(factor=2.5, original=128, fast=24.0, slow=1.5)),
                    latent2=dict(heads=4, dim=64, rot_dim=32, vdim=64, kv_rank=96, scale=0.1, base=1e4),
                    moe=dict(ff=64, experts=8, identity=2, top=2, scale=2.0, shared=128)),
+    # a width that is odd (no vector path anywhere, every GEMM off the tensor-core tiles), tiny feed-forwards
+    "narrow": dict(width=51, vocab=101, side=3, layers=("latent", "gla", "latent2"), ffs=("moe", "dense", "moe"), dense_ff=30,
+                   moe=dict(ff=10, experts=3, identity=1, top=2, scale=1.1, shared=6)),
     # sizes off every tile: odd counts of heads and experts, head sizes that are no multiples of 8 (key rows of 4 k + 2 columns
     # run on the one-query kernel), more identity than real experts
     "odd": dict(vocab=333, width=72, layers=("latent", "gla", "latent2"), ffs=("moe", "dense", "moe"), side=5, rank=3, dense_ff=100,
