@@ -325,9 +325,12 @@ def test_latent_attention_long_context_on_the_tensor_cores(tmp_path):
         assert (got - want).pow(2).mean().sqrt() < 6e-3 * scale, cuts[:4]
 
 
-def test_latent_attention_batches_on_the_tensor_cores(tmp_path):
-    """Several sequences of unequal lengths in one step (tiles that span sequences) and single-token steps of a batch, bf16."""
-    cfg = O.make_config(layers=("latent",), ffs=(None,), side=0, latent=dict(heads=7, dim=24, rot_dim=24, vdim=40, kv_rank=112, scale=0.2, scaling=None))
+@pytest.mark.parametrize("sizes", [dict(heads=7, dim=24, rot_dim=24, vdim=40, kv_rank=112), dict(heads=5, dim=16, rot_dim=24, vdim=16, kv_rank=232),
+                                   dict(heads=18, dim=8, rot_dim=16, vdim=8, kv_rank=320)])
+def test_latent_attention_batches_on_the_tensor_cores(tmp_path, sizes):
+    """Several sequences of unequal lengths in one step (tiles that span sequences) and single-token steps of a batch, bf16; for
+    the 64-key and the 32-key prompt kernels, 128 and 256 value columns per block, more than 16 heads."""
+    cfg = O.make_config(layers=("latent",), ffs=(None,), side=0, latent=dict(scale=0.2, scaling=None, **sizes))
     W = O.random_weights(cfg, seed=3)
     m = cfg["layers"][0]["mixer"]
     Wd = {k: v.double() for k, v in W.items()}
@@ -354,7 +357,7 @@ def test_latent_attention_batches_on_the_tensor_cores(tmp_path):
             for col, n_, src in ((cq, nq, 0), (cd, nd, 1), (cg, ng, 2)):
                 U[o:o + cnt[i], col:col + n_] = data[i][src][a:a + cnt[i]].cuda()
             o += cnt[i]
-        out = torch.empty(T, 7 * 40, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(T, sizes["heads"] * sizes["vdim"], device="cuda", dtype=torch.bfloat16)
         eng._latent_attention(M, U, plan, 1e-5, out)
         o = 0
         for i in use:
@@ -370,7 +373,7 @@ def test_latent_attention_batches_on_the_tensor_cores(tmp_path):
         for r, i in enumerate(use):
             for col, n_, src in ((cq, nq, 0), (cd, nd, 1), (cg, ng, 2)):
                 U[r, col:col + n_] = data[i][src][done[i]].cuda()
-        out = torch.empty(T, 7 * 40, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(T, sizes["heads"] * sizes["vdim"], device="cuda", dtype=torch.bfloat16)
         eng._latent_attention(M, U, plan, 1e-5, out)
         for r, i in enumerate(use):
             got[i].append(out[r:r + 1].double().cpu())
