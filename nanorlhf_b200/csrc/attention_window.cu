@@ -31,6 +31,13 @@ __device__ __forceinline__ int first_key(int p, int window, int chunked) {
   return p - window + 1 > 0 ? p - window + 1 : 0;
 }
 __device__ __forceinline__ float sigmoid_(float z) { return 1.f / (1.f + expf(-z)); }
+// a scaled score with the optional terms: cap, then distance slope and distance bias (neither is scaled or capped)
+__device__ __forceinline__ float score_terms(float sc, int dist, int h, int Hq, float slope, const NrlAttnMods& md) {
+  if (md.softcap > 0.f) sc = md.softcap * tanhf(sc / md.softcap);
+  sc -= slope * static_cast<float>(dist);
+  if (md.dist_bias != nullptr) sc += md.dist_bias[static_cast<long>(dist < md.dist_max ? dist : md.dist_max) * Hq + h];
+  return sc;
+}
 
 // warp per (token, key/value head): keys and (optionally blended) values into the pages
 template <typename CT>
@@ -184,7 +191,9 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
   for (int c = threadIdx.x; c < D; c += blockDim.x) sq_[c] = q[t * sq + static_cast<long>(h) * (md.q_head_stride ? md.q_head_stride : D) + c];
   __syncthreads();
   const int lo = first_key(p, window, md.chunked);
-  const int nkeys = p - lo + 1;
+  const int kf = (!md.chunked && md.keep_first > 0) ? min(md.keep_first, lo) : 0;    // kept first keys in front of the window
+  const int nkeys = kf + p - lo + 1;
+  const int Hv = md.v_div > 1 ? Hkv / md.v_div : Hkv, gv = md.v_div > 1 ? g / md.v_div : g;
   if (md.head_scale != nullptr) scale *= md.head_scale[h];
   const float slope = md.head_slope != nullptr ? md.head_slope[h] : 0.f;
   if (md.gate != nullptr) out_scale *= sigmoid_(md.gate[t * md.gate_stride + h]);
@@ -193,8 +202,9 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
 #pragma unroll
   for (int i = 0; i < kMaxDvPerLane; ++i) acc[i] = 0.f;
   for (int base = w * 32; base < nkeys; base += kWarps * 32) {
-    const int j = lo + base + lane;
-    const bool ok = base + lane < nkeys;
+    const int vi = base + lane;
+    const int j = vi < kf ? vi : lo + vi - kf;
+    const bool ok = vi < nkeys;
     float sc = -INFINITY;
     long vrow = 0;
     if (ok) {
@@ -203,8 +213,8 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
       const CT* kr = k_cache + cell * D;
       float d = 0.f;
       for (int c = 0; c < D; ++c) d += sq_[c] * ld(kr, c);
-      sc = d * scale - slope * static_cast<float>(p - j);
-      vrow = cell * (md.kv_shared ? D : Dv);
+      sc = score_terms(d * scale, p - j, h, Hq, slope, md);
+      vrow = md.kv_shared ? cell * D : ((pg * Hv + gv) * page + (j % page)) * Dv;
     }
     const float mn = fmaxf(m, warp_max(sc));
     const float corr = expf(m - mn);               // m = -inf on the first run: exp(-inf) = 0
@@ -306,7 +316,9 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
     const int nt = tn - t, nqs = nt * hb;
     const int p_first = pos[t];
     const int lo = first_key(p_first, window, md.chunked);       // the first key of a run's first token: later tokens start no earlier
-    const int nkeys = p_first + nt - lo;
+    const int keep = md.chunked ? 0 : md.keep_first;
+    const int kf = keep > 0 ? min(keep, lo) : 0;                 // kept first keys in front of the run's window
+    const int nkeys = kf + p_first + nt - lo;
     const int* bt = block_table + static_cast<long>(e) * max_blocks;
     __syncthreads();
     for (int idx = threadIdx.x; idx < NQ * D; idx += blockDim.x) {
@@ -322,6 +334,8 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
     __syncthreads();
     float m[NQ], l[NQ], acc[NQ][4 * NVC], slope[NQ];
     const long vstride = md.kv_shared ? D : Dv;
+    const int Hv = md.v_div > 1 ? Hkv / md.v_div : Hkv, gv = md.v_div > 1 ? g / md.v_div : g;
+    const bool terms = md.softcap > 0.f || md.dist_bias != nullptr;
 #pragma unroll
     for (int i = 0; i < NQ; ++i) {
       slope[i] = (md.head_slope != nullptr && i < nqs) ? md.head_slope[h0 + i % hb] : 0.f;
@@ -331,14 +345,17 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
       for (int x = 0; x < 4 * NVC; ++x) acc[i][x] = 0.f;
     }
     for (int base = w * 32; base < nkeys; base += kWarps * 32) {
-      const int j = lo + base + lane;
-      const bool ok = base + lane < nkeys;
+      const int vi = base + lane;
+      const int j = vi < kf ? vi : lo + vi - kf;
+      const bool ok = vi < nkeys;
       float s[NQ];
 #pragma unroll
       for (int i = 0; i < NQ; ++i) s[i] = 0.f;
-      long cell = 0;
+      long cell = 0, vcell = 0;
       if (ok) {
-        cell = (static_cast<long>(bt[j / page]) * Hkv + g) * page + (j % page);
+        const long pgj = bt[j / page];
+        cell = (pgj * Hkv + g) * page + (j % page);
+        vcell = md.kv_shared ? cell : (pgj * Hv + gv) * page + (j % page);
         const CT* kr = k_cache + cell * D;
         if (vec8) {
           for (int c = 0; c < D; c += 8) {
@@ -361,8 +378,9 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
 #pragma unroll
       for (int i = 0; i < NQ; ++i) {
         const int pq = p_first + i / hb;                                   // position of query i
-        const bool valid = ok && i < nqs && j <= pq && j >= first_key(pq, window, md.chunked);
-        const float sc = valid ? s[i] - slope[i] * static_cast<float>(pq - j) : -INFINITY;
+        const bool valid = ok && i < nqs && j <= pq && (j >= first_key(pq, window, md.chunked) || j < keep);
+        float sc = -INFINITY;
+        if (valid) sc = terms ? score_terms(s[i], pq - j, h0 + i % hb, Hq, slope[i], md) : s[i] - slope[i] * static_cast<float>(pq - j);
         const float mn = fmaxf(m[i], warp_max(sc));
         float pr = 0.f;
         if (mn != -INFINITY) {                                              // some key of this query has been seen
@@ -378,7 +396,7 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
       __syncwarp();
       const int cnt = nkeys - base < 32 ? nkeys - base : 32;
       for (int jj = 0; jj < cnt; ++jj) {
-        const long vr = __shfl_sync(0xffffffffu, cell, jj) * vstride;
+        const long vr = __shfl_sync(0xffffffffu, vcell, jj) * vstride;
 #pragma unroll
         for (int x = 0; x < NVC; ++x) {
           const int c0 = lane * 4 + 128 * x;
@@ -472,6 +490,114 @@ cudaError_t launch_tile_nq(int nq, const float* q, long sq, const void* k_cache,
 #undef NRL_WA
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Write side of rotated attention, one launch per step: warp per (token, vector).  Vectors 0 .. Hq-1 are the query heads
+// (float, finished in place), Hq .. Hq+Hk-1 the key heads (finished into their page), then Hv value heads (copied into their
+// page; v == nullptr: the values are the keys as projected, bias included, before rotation and norm, written by the key's warp).
+// A vector is staged in shared memory: + bias, the first `rdims` columns rotated by the angles pos * freq[i] (formed and reduced
+// to [-pi, pi] in double; cos and sin times `mult`; interleaved pairs (2i, 2i + 1), else (i, i + rdims / 2)), then, with
+// unit_norm, divided by its root mean square (eps inside the root; times norm_w [D] when given).  k == nullptr: queries only
+// (a layer that reads another layer's pages).
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kRotWarps = 4;
+
+template <typename CT>
+__global__ void rot_kv_write_kernel(float* __restrict__ q, long sq, const float* __restrict__ q_bias, const float* __restrict__ k, long sk,
+                                    const float* __restrict__ k_bias, const float* __restrict__ v, long sv, const double* __restrict__ freq,
+                                    int rdims, float mult, int interleaved, int unit_norm, const float* __restrict__ q_norm_w,
+                                    const float* __restrict__ k_norm_w, float eps, const int* __restrict__ pos,
+                                    const int* __restrict__ kv_slot, CT* __restrict__ k_cache, CT* __restrict__ v_cache, int page, long T,
+                                    int Hq, int Hk, int Hv, int D, int Dv) {
+  extern __shared__ float rot_stage[];                      // [kRotWarps][D]
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const long wid = blockIdx.x * static_cast<long>(kRotWarps) + w;
+  const int nk = k != nullptr ? Hk : 0, nv = (k != nullptr && v != nullptr) ? Hv : 0;
+  const int per = Hq + nk + nv;
+  if (wid >= T * per) return;
+  const long t = wid / per;
+  const int vec = static_cast<int>(wid - t * per);
+  const int slot = k != nullptr ? kv_slot[t] : 0;
+  const long pg = slot / page, off = slot % page;
+  if (vec >= Hq + nk) {                                      // a value head: plain copy
+    const int g = vec - Hq - nk;
+    const float* x = v + t * sv + static_cast<long>(g) * Dv;
+    CT* dst = v_cache + ((pg * Hv + g) * page + off) * Dv;
+    for (int c = lane; c < Dv; c += 32) st(dst, c, x[c]);
+    return;
+  }
+  const bool is_q = vec < Hq;
+  const int hd = is_q ? vec : vec - Hq;
+  const float* src = is_q ? q + t * sq + static_cast<long>(hd) * D : k + t * sk + static_cast<long>(hd) * D;
+  const float* bias = is_q ? q_bias : k_bias;
+  float* x = rot_stage + w * D;
+  for (int c = lane; c < D; c += 32) x[c] = src[c] + (bias != nullptr ? bias[static_cast<long>(hd) * D + c] : 0.f);
+  __syncwarp();
+  if (!is_q && v == nullptr) {                               // the values are the keys as projected
+    CT* dst = v_cache + ((pg * Hk + hd) * page + off) * D;
+    for (int c = lane; c < D; c += 32) st(dst, c, x[c]);
+  }
+  const double p = static_cast<double>(pos[t]);
+  const int half = rdims / 2;
+  for (int i = lane; i < half; i += 32) {
+    double a = p * freq[i];
+    a -= 6.283185307179586476925 * rint(a * 0.15915494309189533577);
+    float sn, cs;
+    sincosf(static_cast<float>(a), &sn, &cs);
+    sn *= mult;
+    cs *= mult;
+    const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
+    const float u = x[iu], vv = x[iv];
+    x[iu] = u * cs - vv * sn;
+    x[iv] = vv * cs + u * sn;
+  }
+  __syncwarp();
+  float r = 1.f;
+  const float* nw = nullptr;
+  if (unit_norm) {
+    float ss = 0.f;
+    for (int c = lane; c < D; c += 32) ss += x[c] * x[c];
+    ss = warp_sum(ss);
+    r = 1.f / sqrtf(ss / static_cast<float>(D) + eps);
+    nw = is_q ? q_norm_w : k_norm_w;
+  }
+  if (is_q) {
+    float* dst = q + t * sq + static_cast<long>(hd) * D;
+    for (int c = lane; c < D; c += 32) dst[c] = x[c] * r * (nw != nullptr ? nw[c] : 1.f);
+  } else {
+    CT* dst = k_cache + ((pg * Hk + hd) * page + off) * D;
+    for (int c = lane; c < D; c += 32) st(dst, c, x[c] * r * (nw != nullptr ? nw[c] : 1.f));
+  }
+}
+
+// Differential attention, read side: a [T, maps * H, Dv] (typed) holds the outputs of two score maps over the same values, the heads
+// ordered (key/value head g, map m, query head r of the group): o = a_1 - lambda a_2, divided by its root mean square over the
+// head's Dv values (eps inside the root), times post, times sigmoid(gate[t, h * Dv + c]) (gate float or null), times out_scale.
+// warp per (token, head); out typed [T, H * Dv] in the model's head order h = g * R + r.
+template <typename AT, typename OT>
+__global__ void diff_combine_kernel(const AT* __restrict__ a, long sa, float lambda, float post, float eps, const float* __restrict__ gate,
+                                    long sg, float out_scale, OT* __restrict__ out, long so, long T, int H, int R, int Dv) {
+  const long wid = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= T * H) return;
+  const long t = wid / H;
+  const int h = static_cast<int>(wid - t * H), g = h / R, r = h % R;
+  const AT* a1 = a + t * sa + (static_cast<long>(2 * g) * R + r) * Dv;
+  const AT* a2 = a + t * sa + (static_cast<long>(2 * g + 1) * R + r) * Dv;
+  float ss = 0.f;
+  for (int c = lane; c < Dv; c += 32) {
+    const float o = ld(a1, c) - lambda * ld(a2, c);
+    ss += o * o;
+  }
+  ss = warp_sum(ss);
+  const float f = post * out_scale / sqrtf(ss / static_cast<float>(Dv) + eps);
+  for (int c = lane; c < Dv; c += 32) {
+    const long col = static_cast<long>(h) * Dv + c;
+    float o = (ld(a1, c) - lambda * ld(a2, c)) * f;
+    if (gate != nullptr) o *= sigmoid_(gate[t * sg + col]);
+    st(out, t * so + col, o);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -534,14 +660,15 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
   NrlAttnMods md = {0, nullptr, nullptr, nullptr, 0};
   if (mods != nullptr) md = *mods;
   if (md.kv_shared && (Dv > D || v_cache != k_cache)) return cudaErrorInvalidValue;
+  if (md.v_div > 1 && (Hkv % md.v_div != 0 || md.kv_shared)) return cudaErrorInvalidValue;
+  if (md.dist_bias != nullptr && md.dist_max < 0) return cudaErrorInvalidValue;
   // latent attention (one shared row per token is key and value of every head, causal) over bf16 pages: its own tensor-core kernels
   if ((impl == 0 || impl == 3) && !cache_f32 && md.kv_shared && Hkv == 1 && window >= (1 << 30) && !md.chunked &&
       md.head_scale == nullptr && md.head_slope == nullptr && nrl_latent_attention_mma_fits(out, so, D, Dv, page))
     return nrl_latent_attention_mma(q, sq, k_cache, block_table, max_blocks, tok_entry, pos, scale, out_scale, out, so, T, Hq, D, Dv, page,
                                     single_token, nsplit, part, &md, s);
   // prompt portions over bf16 pages: tensor cores
-  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) &&
-      md.head_sink == nullptr && !md.kv_shared) {
+  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) && !md.kv_shared) {
     if (single_token && nsplit >= 1 && part != nullptr)
       return nrl_window_attention_decode(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out,
                                          so, T, Hq, Hkv, D, Dv, page, nsplit, part, &md, s);
@@ -568,6 +695,48 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
     window_attention_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kWarps * 32, smem, s>>>(
         q, sq, static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache), block_table, max_blocks,
         tok_entry, pos, window, scale, out_scale, static_cast<__nv_bfloat16*>(out), so, Hq, Hkv, D, Dv, page, md);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_rot_kv_write(float* q, long sq, const float* q_bias, const float* k, long sk, const float* k_bias, const float* v, long sv,
+                             const double* freq, int rdims, float mult, int interleaved, int unit_norm, const float* q_norm_w,
+                             const float* k_norm_w, float eps, const int* pos, const int* kv_slot, void* k_cache, void* v_cache,
+                             int cache_f32, int page, int T, int Hq, int Hk, int Hv, int D, int Dv, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (rdims < 0 || rdims > D || rdims % 2 != 0 || (rdims > 0 && freq == nullptr) || D < 1 || D > 2048) return cudaErrorInvalidValue;
+  if (k != nullptr && v == nullptr && (Hv != Hk || Dv != D)) return cudaErrorInvalidValue;
+  const int per = Hq + (k != nullptr ? Hk + (v != nullptr ? Hv : 0) : 0);
+  const long warps = static_cast<long>(T) * per;
+  const unsigned blocks = static_cast<unsigned>((warps + kRotWarps - 1) / kRotWarps);
+  const size_t smem = sizeof(float) * kRotWarps * D;
+  if (cache_f32)
+    rot_kv_write_kernel<float><<<blocks, kRotWarps * 32, smem, s>>>(q, sq, q_bias, k, sk, k_bias, v, sv, freq, rdims, mult, interleaved,
+                                                                    unit_norm, q_norm_w, k_norm_w, eps, pos, kv_slot,
+                                                                    static_cast<float*>(k_cache), static_cast<float*>(v_cache), page, T, Hq,
+                                                                    Hk, Hv, D, Dv);
+  else
+    rot_kv_write_kernel<__nv_bfloat16><<<blocks, kRotWarps * 32, smem, s>>>(q, sq, q_bias, k, sk, k_bias, v, sv, freq, rdims, mult,
+                                                                            interleaved, unit_norm, q_norm_w, k_norm_w, eps, pos, kv_slot,
+                                                                            static_cast<__nv_bfloat16*>(k_cache),
+                                                                            static_cast<__nv_bfloat16*>(v_cache), page, T, Hq, Hk, Hv, D, Dv);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_diff_combine(const void* a, long sa, int a_f32, float lambda, float post, float eps, const float* gate, long sg,
+                             float out_scale, void* out, long so, int out_f32, int T, int H, int Hkv, int Dv, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (Hkv < 1 || H % Hkv != 0) return cudaErrorInvalidValue;
+  const long warps = static_cast<long>(T) * H;
+  const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
+  const int R = H / Hkv;
+#define NRL_DC(AT_, OT_)                                                                                                           \
+  diff_combine_kernel<AT_, OT_><<<blocks, 128, 0, s>>>(static_cast<const AT_*>(a), sa, lambda, post, eps, gate, sg, out_scale,       \
+                                                       static_cast<OT_*>(out), so, T, H, R, Dv)
+  if (a_f32 && out_f32) NRL_DC(float, float);
+  else if (a_f32) NRL_DC(float, __nv_bfloat16);
+  else if (out_f32) NRL_DC(__nv_bfloat16, float);
+  else NRL_DC(__nv_bfloat16, __nv_bfloat16);
+#undef NRL_DC
   return cudaGetLastError();
 }
 

@@ -1,5 +1,7 @@
 // Sliding-window (or chunked) attention on the tensor cores, reading the 16-token bf16 pages in place.  The optional terms of
-// NrlAttnMods (chunk mask, per-head score multiplier and distance slope, per-head output gate) are applied in float.
+// NrlAttnMods (chunk mask, per-head score multiplier and distance slope, per-head output gate, capped scores, a bias per distance,
+// first keys that stay visible behind the window, a sink in the denominator, several key heads over one value head) are applied
+// in float.
 //
 // Prompt portions (window_attention_mma_kernel): a block owns 64 query rows that share one key/value head -- QT
 // consecutive tokens x HB query heads -- as four warps of 16 rows, and walks the keys its rows can see in blocks of 64
@@ -51,6 +53,13 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
+}
+
+// cap * tanh(x / cap) through 2^x on the special-function unit: tanh(z) = (1 - e) / (1 + e), e = exp(-2 |z|) (relative error of a
+// few 2^-22: far below the bf16 rounding of the weights that follow)
+__device__ __forceinline__ float softcap_(float x, float cap, float inv_cap) {
+  const float e = ex2(-2.885390081777927f * fabsf(x * inv_cap));
+  return copysignf(cap * __fdividef(1.f - e, 1.f + e), x);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -147,6 +156,26 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     slr[hf] = md.head_slope != nullptr ? md.head_slope[hq] * 1.4426950408889634f : 0.f;
   }
   const bool sloped = md.head_slope != nullptr;
+  // capped scores and a bias per distance work on the natural-log score of every element: no shortcut for interior blocks
+  const bool terms = md.softcap > 0.f || md.dist_bias != nullptr;
+  float sc_nat[2];
+  int hq_row[2];
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    hq_row[hf] = min(h0 + (w * 16 + gq + hf * 8) % HB, Hq - 1);
+    sc_nat[hf] = scale * (md.head_scale != nullptr ? md.head_scale[hq_row[hf]] : 1.f);
+  }
+  const int keep = md.chunked ? 0 : md.keep_first;          // keys below `keep` stay visible behind the window
+  const int Hv = md.v_div > 1 ? Hkv / md.v_div : Hkv, gv = md.v_div > 1 ? g / md.v_div : g;
+  const float inv_cap = md.softcap > 0.f ? 1.f / md.softcap : 0.f;
+  const float* brow[2] = {md.dist_bias != nullptr ? md.dist_bias + hq_row[0] : nullptr, md.dist_bias != nullptr ? md.dist_bias + hq_row[1] : nullptr};
+  // one score with its terms, natural-log domain in, log2 domain out (the slope is already in the log2 domain)
+  auto with_terms = [&](float raw, int hf, int dist) {
+    float x = raw * sc_nat[hf];
+    if (md.softcap > 0.f) x = softcap_(x, md.softcap, inv_cap);
+    if (md.dist_bias != nullptr) x += __ldg(brow[hf] + min(max(dist, 0), md.dist_max) * Hq);
+    return x * 1.4426950408889634f - slr[hf] * static_cast<float>(dist);
+  };
 
   int t = t_begin;
   while (t < t_end) {
@@ -157,7 +186,10 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     const int lo = max(0, first_key(p_first, window, md.chunked)), hi = p_first + (tn - t) - 1;
     const int* bt = block_table + static_cast<long>(e) * max_blocks;
     const int kb0 = (lo / kBN) * kBN;
-    const int nblk = (hi - kb0) / kBN + 1;
+    // blocks of kept first keys in front of the window's blocks (they end at or before kb0: no key is walked twice)
+    const int nkb = keep > 0 ? (min(keep, kb0) + kBN - 1) / kBN : 0;
+    const int nblk = nkb + (hi - kb0) / kBN + 1;
+    auto block_start = [&](int ib) { return ib < nkb ? ib * kBN : kb0 + (ib - nkb) * kBN; };
     // positions of this thread's rows inside the run (or "not in this run")
     int pq[2], plo[2];
     bool act[2];
@@ -176,24 +208,25 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
 
     __syncthreads();                                       // the previous run's last block has been consumed
     int pg[4];
-    block_pages(bt, kb0, hi, pg);
-    load_kv_block<DP>(sK, k_cache, pg, Hkv, g, kb0, hi, D);
-    load_kv_block<DVP>(sV, v_cache, pg, Hkv, g, kb0, hi, Dv);
+    block_pages(bt, block_start(0), hi, pg);
+    load_kv_block<DP>(sK, k_cache, pg, Hkv, g, block_start(0), hi, D);
+    load_kv_block<DVP>(sV, v_cache, pg, Hv, gv, block_start(0), hi, Dv);
     cp_commit();
-    if (nblk > 1) block_pages(bt, kb0 + kBN, hi, pg);       // page ids are fetched a block ahead of their use
+    if (nblk > 1) block_pages(bt, block_start(1), hi, pg);  // page ids are fetched a block ahead of their use
     for (int ib = 0; ib < nblk; ++ib) {
-      const int kb = kb0 + ib * kBN, buf = ib & 1;
+      const int kb = block_start(ib), buf = ib & 1;
       if (ib + 1 < nblk) {
-        load_kv_block<DP>(sK + (buf ^ 1) * kBN * LDK, k_cache, pg, Hkv, g, kb + kBN, hi, D);
-        load_kv_block<DVP>(sV + (buf ^ 1) * kBN * LDV, v_cache, pg, Hkv, g, kb + kBN, hi, Dv);
+        const int kn = block_start(ib + 1);
+        load_kv_block<DP>(sK + (buf ^ 1) * kBN * LDK, k_cache, pg, Hkv, g, kn, hi, D);
+        load_kv_block<DVP>(sV + (buf ^ 1) * kBN * LDV, v_cache, pg, Hv, gv, kn, hi, Dv);
         cp_commit();
-        if (ib + 2 < nblk) block_pages(bt, kb + 2 * kBN, hi, pg);
+        if (ib + 2 < nblk) block_pages(bt, block_start(ib + 2), hi, pg);
         cp_wait<1>();
       } else {
         cp_wait<0>();
       }
       __syncthreads();
-      if (warp_in && kb <= whi && kb + kBN - 1 >= wlo) {
+      if (warp_in && kb <= whi && (kb + kBN - 1 >= wlo || kb < keep)) {
         const __nv_bfloat16* bK = sK + buf * kBN * LDK;
         const __nv_bfloat16* bV = sV + buf * kBN * LDV;
         float s[8][4];
@@ -216,7 +249,17 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
         // scale (log2 domain), mask, online softmax (float).  A block that every row of the warp sees whole needs no mask.
         const bool interior = !sloped && warp_full && kb + kBN - 1 <= p_first + (wt_lo - t) && kb >= whi_lo;
         float mx[2] = {-INFINITY, -INFINITY};
-        if (interior) {
+        if (interior && terms) {                           // every key is seen by every row: the terms without the mask
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int hf = i >> 1;
+              s[n][i] = with_terms(s[n][i], hf, pq[hf] - (kb + n * 8 + 2 * tq + (i & 1)));
+              mx[hf] = fmaxf(mx[hf], s[n][i]);
+            }
+          }
+        } else if (interior) {
 #pragma unroll
           for (int n = 0; n < 8; ++n) {
 #pragma unroll
@@ -231,8 +274,13 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int hf = i >> 1, j = kb + n * 8 + 2 * tq + (i & 1);
-              const bool valid = act[hf] && j <= pq[hf] && j >= plo[hf];
-              const float sc = valid ? s[n][i] * sl2[hf] - slr[hf] * static_cast<float>(pq[hf] - j) : -INFINITY;
+              const bool valid = act[hf] && j <= pq[hf] && (j >= plo[hf] || j < keep);
+              float sc = -INFINITY;
+              if (valid && !terms) {
+                sc = s[n][i] * sl2[hf] - slr[hf] * static_cast<float>(pq[hf] - j);
+              } else if (valid) {
+                sc = with_terms(s[n][i], hf, pq[hf] - j);
+              }
               s[n][i] = sc;
               mx[hf] = fmaxf(mx[hf], sc);
             }
@@ -297,6 +345,11 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     const int r = w * 16 + gq + hf * 8;
     __nv_bfloat16* dst = out + static_cast<long>(row_t[hf]) * so + static_cast<long>(h0 + r % HB) * Dv;
     float f = out_scale / l;
+    if (md.head_sink != nullptr) {                         // one more term in the denominator: a score with no key and no value
+      const float s2 = md.head_sink[h0 + r % HB] * 1.4426950408889634f, mt = fmaxf(m_run[hf], s2);
+      const float fo = ex2(m_run[hf] - mt);
+      f = out_scale * fo / (l * fo + ex2(s2 - mt));
+    }
     if (md.gate != nullptr) f *= sigmoid_(md.gate[static_cast<long>(row_t[hf]) * md.gate_stride + h0 + r % HB]);
 #pragma unroll
     for (int i = 0; i < 2 * NV; ++i) {
@@ -346,14 +399,20 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
   const int p = pos[t];
   const int lo = max(0, first_key(p, window, md.chunked));
   const int* bt = block_table + static_cast<long>(tok_entry[t]) * max_blocks;
-  const int pg_first = lo >> 4, npages = (p >> 4) - pg_first + 1;
+  const int keep = md.chunked ? 0 : md.keep_first;          // keys below `keep` stay visible behind the window
+  const int Hv = md.v_div > 1 ? Hkv / md.v_div : Hkv, gv = md.v_div > 1 ? g / md.v_div : g;
+  // the walk: pages of kept first keys in front of the window's pages; a walk index below nkp is a kept page
+  const int pg_first = lo >> 4, nkp = keep > 0 ? min((keep + 15) >> 4, pg_first) : 0, npages = nkp + (p >> 4) - pg_first + 1;
   const int per_part = (npages + nparts - 1) / nparts;
-  const int pg0 = pg_first + pi * per_part, pg1 = min(pg_first + npages, pg0 + per_part);     // this warp's pages [pg0, pg1)
+  const int pg0 = pi * per_part, pg1 = min(npages, pg0 + per_part);     // this warp's walk indices [pg0, pg1)
+  auto page_of = [&](int wi) { return wi < nkp ? wi : pg_first + wi - nkp; };
 
-  auto load_page = [&](int stage, int pg) {
+  auto load_page = [&](int stage, int wi) {
+    const int pg = page_of(wi);
     __nv_bfloat16* sK = ring + stage * kStageElems;
     __nv_bfloat16* sV = sK + 16 * LDK;
     const long cell0 = (static_cast<long>(bt[pg]) * Hkv + g) * 16;
+    const long vcell0 = (static_cast<long>(bt[pg]) * Hv + gv) * 16;
     constexpr int kch = DP / 8, vch = DVP / 8;              // powers of two: shifts
 #pragma unroll
     for (int idx = lane; idx < 16 * kch; idx += 32) {
@@ -366,7 +425,7 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
     for (int idx = lane; idx < 16 * vch; idx += 32) {
       const int key = idx / vch, ch = idx % vch;
       __nv_bfloat16* d = sV + key * LDV + ch * 8;
-      if (pg * 16 + key <= p && ch * 8 < Dv) cp_async16(smem_u32(d), v_cache + (cell0 + key) * Dv + ch * 8);
+      if (pg * 16 + key <= p && ch * 8 < Dv) cp_async16(smem_u32(d), v_cache + (vcell0 + key) * Dv + ch * 8);
       else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
     }
   };
@@ -375,11 +434,15 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
 #pragma unroll
   for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float sl2[2], slr[2];                                    // per row (= query head), log2 domain
+  float sl2[2], slr[2], sc_nat[2];                         // per row (= query head); sl2 / slr in the log2 domain
+  int hq_row[2];
+  const bool terms = md.softcap > 0.f || md.dist_bias != nullptr;
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
     const int hq = min(h0 + gq + hf * 8, Hq - 1);
-    sl2[hf] = scale * 1.4426950408889634f * (md.head_scale != nullptr ? md.head_scale[hq] : 1.f);
+    hq_row[hf] = hq;
+    sc_nat[hf] = scale * (md.head_scale != nullptr ? md.head_scale[hq] : 1.f);
+    sl2[hf] = sc_nat[hf] * 1.4426950408889634f;
     slr[hf] = md.head_slope != nullptr ? md.head_slope[hq] * 1.4426950408889634f : 0.f;
   }
 #pragma unroll
@@ -387,9 +450,10 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
     if (pg0 + i < pg1) load_page(i, pg0 + i);
     cp_commit();
   }
-  for (int pg = pg0; pg < pg1; ++pg) {
-    const int stage = (pg - pg0) % kDecStages;
-    if (pg + kDecStages - 1 < pg1) load_page((pg - pg0 + kDecStages - 1) % kDecStages, pg + kDecStages - 1);
+  for (int wi = pg0; wi < pg1; ++wi) {
+    const int pg = page_of(wi);
+    const int stage = (wi - pg0) % kDecStages;
+    if (wi + kDecStages - 1 < pg1) load_page((wi - pg0 + kDecStages - 1) % kDecStages, wi + kDecStages - 1);
     cp_commit();
     cp_wait<kDecStages - 1>();
     __syncwarp();
@@ -412,8 +476,17 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
     for (int n = 0; n < 2; ++n) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int j = pg * 16 + n * 8 + 2 * tq + (i & 1);
-        const float sc = (j <= p && j >= lo) ? s[n][i] * sl2[i >> 1] - slr[i >> 1] * static_cast<float>(p - j) : -INFINITY;
+        const int j = pg * 16 + n * 8 + 2 * tq + (i & 1), hf = i >> 1;
+        const bool valid = j <= p && (j >= lo || j < keep);
+        float sc = -INFINITY;
+        if (valid && !terms) {
+          sc = s[n][i] * sl2[hf] - slr[hf] * static_cast<float>(p - j);
+        } else if (valid) {
+          float x = s[n][i] * sc_nat[hf];
+          if (md.softcap > 0.f) x = softcap_(x, md.softcap, 1.f / md.softcap);
+          if (md.dist_bias != nullptr) x += __ldg(md.dist_bias + static_cast<long>(min(p - j, md.dist_max)) * Hq + hq_row[hf]);
+          sc = x * 1.4426950408889634f - slr[hf] * static_cast<float>(p - j);
+        }
         s[n][i] = sc;
         mrow[i >> 1] = fmaxf(mrow[i >> 1], sc);
       }
@@ -486,14 +559,16 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
 
 // block per (token, query head): out = out_scale * sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s
 __global__ void window_attention_merge_kernel(const float* __restrict__ part, int nsplit, int Hq, int Dv, float out_scale,
-                                              __nv_bfloat16* __restrict__ out, long so, const float* __restrict__ gate, long gate_stride) {
+                                              __nv_bfloat16* __restrict__ out, long so, const float* __restrict__ gate, long gate_stride,
+                                              const float* __restrict__ head_sink) {
   const long t = blockIdx.x;
   const int h = blockIdx.y;
   if (gate != nullptr) out_scale *= sigmoid_(gate[t * gate_stride + h]);
   const float* p = part + (t * Hq + h) * nsplit * (Dv + 2);
-  float M = -INFINITY;
+  const float sink2 = head_sink != nullptr ? head_sink[h] * 1.4426950408889634f : -INFINITY;   // the sink joins as a part without values
+  float M = sink2;
   for (int x = 0; x < nsplit; ++x) M = fmaxf(M, p[x * (Dv + 2) + Dv]);
-  float L = 0.f;
+  float L = head_sink != nullptr ? ex2(sink2 - M) : 0.f;
   for (int x = 0; x < nsplit; ++x) {
     const float m = p[x * (Dv + 2) + Dv];
     if (m != -INFINITY) L += ex2(m - M) * p[x * (Dv + 2) + Dv + 1];
@@ -551,7 +626,7 @@ cudaError_t launch_decode(const float* q, long sq, const void* k_cache, const vo
   if (e != cudaSuccess) return e;
   window_attention_merge_kernel<<<dim3(T, Hq), Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128, 0, s>>>(part, nsplit * 4, Hq, Dv, out_scale,
                                                                                           static_cast<__nv_bfloat16*>(out), so, md.gate,
-                                                                                          md.gate_stride);
+                                                                                          md.gate_stride, md.head_sink);
   return cudaGetLastError();
 }
 

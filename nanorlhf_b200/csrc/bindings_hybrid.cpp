@@ -173,7 +173,7 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
                       const Tensor& pos, int64_t window, double scale, double out_scale, Tensor out, int64_t impl, bool chunked,
                       const c10::optional<Tensor>& head_scale, const c10::optional<Tensor>& head_slope,
                       const c10::optional<Tensor>& gate, const c10::optional<Tensor>& head_sink, bool kv_shared, int64_t value_size,
-                      int64_t heads) {
+                      int64_t heads, double softcap, int64_t keep_first, const c10::optional<Tensor>& dist_bias, int64_t v_div) {
   const bool single_token = block_table.size(0) == (q.dim() == 3 ? q.size(1) : q.size(0));
   c10::cuda::CUDAGuard guard(q.device());
   const int Hkv = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
@@ -210,11 +210,25 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
     md.gate = f32(*gate, "gate");
     md.gate_stride = gate->stride(0);
   }
+  md.softcap = static_cast<float>(softcap);
+  md.keep_first = static_cast<int>(keep_first);
+  if (dist_bias.has_value()) {
+    TORCH_CHECK(dist_bias->dim() == 2 && dist_bias->size(1) == Hq && dist_bias->size(0) >= 1 && dist_bias->is_contiguous(),
+                "window_attention: dist_bias [distances, Hq]");
+    md.dist_bias = f32(*dist_bias, "dist_bias");
+    md.dist_max = static_cast<int>(dist_bias->size(0)) - 1;
+  }
+  if (v_div > 1) {
+    TORCH_CHECK(!kv_shared && Hkv % v_div == 0 && v_cache.size(1) * v_div == Hkv, "window_attention: v_div key heads share one value head");
+    md.v_div = static_cast<int>(v_div);
+  } else {
+    TORCH_CHECK(kv_shared || v_cache.size(1) == Hkv, "window_attention: key and value heads differ");
+  }
   // steps of single tokens on bf16 pages: cut the key walk into parts so that few sequences still fill the GPU
   int nsplit = 0;
   Tensor part;
   if (single_token && (impl == 0 || impl == 3) && k_cache.scalar_type() == at::kBFloat16 &&
-      nrl_window_attention_mma_fits(out.data_ptr(), out.stride(0), Hq, Hkv, D, Dv, page) && md.head_sink == nullptr && !md.kv_shared) {
+      nrl_window_attention_mma_fits(out.data_ptr(), out.stride(0), Hq, Hkv, D, Dv, page) && !md.kv_shared) {
     nsplit = nrl_window_attention_splits(T, Hq, Hkv, static_cast<int>(window), static_cast<int>(block_table.size(1)), page);
     if (nsplit >= 1) part = at::empty({T, Hq, 4 * nsplit, Dv + 2}, q.options().dtype(at::kFloat));
   }
@@ -229,6 +243,123 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
                              out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, static_cast<int>(impl),
                              nsplit, nsplit >= 1 ? part.data_ptr<float>() : nullptr, &md, cur_stream()),
         "window_attention");
+}
+
+void embed_streams(const Tensor& embed, const Tensor& tok, double scale, Tensor xs) {
+  c10::cuda::CUDAGuard guard(xs.device());
+  const int T = static_cast<int>(tok.numel());
+  TORCH_CHECK(embed.dim() == 2 && embed.is_contiguous() && xs.dim() == 3 && xs.is_contiguous() && xs.size(0) == T && xs.size(2) == embed.size(1),
+              "embed_streams: embed [V, W], xs [T, S, W]");
+  check(nrl_embed_streams(embed.data_ptr(), typed(embed, "embed"), i32(tok, "tok"), static_cast<float>(scale), f32w(xs, "xs"), T,
+                          static_cast<int>(xs.size(1)), static_cast<int>(xs.size(2)), cur_stream()),
+        "embed_streams");
+}
+
+void hyper_boundary(Tensor xs, const c10::optional<Tensor>& o, const c10::optional<Tensor>& o_bias, const c10::optional<Tensor>& self_w,
+                    const c10::optional<Tensor>& mix, const c10::optional<Tensor>& outw, const c10::optional<Tensor>& inw,
+                    const c10::optional<Tensor>& ln_w, const c10::optional<Tensor>& ln_b, double eps, c10::optional<Tensor> h) {
+  c10::cuda::CUDAGuard guard(xs.device());
+  TORCH_CHECK(xs.dim() == 3 && xs.is_contiguous(), "hyper_boundary: xs [T, S, W] contiguous");
+  const int T = static_cast<int>(xs.size(0)), S = static_cast<int>(xs.size(1)), W = static_cast<int>(xs.size(2));
+  if (o.has_value()) TORCH_CHECK(o->is_contiguous() && o->dim() == 2 && o->size(0) == T && o->size(1) == W, "hyper_boundary: o [T, W]");
+  if (o_bias.has_value()) TORCH_CHECK(o_bias->numel() == W && o_bias->is_contiguous(), "hyper_boundary: o_bias [W]");
+  if (self_w.has_value()) TORCH_CHECK(self_w->numel() == T && self_w->is_contiguous() && h.has_value(), "hyper_boundary: self_w [T] goes with h");
+  if (mix.has_value()) TORCH_CHECK(mix->numel() == S * S && mix->is_contiguous(), "hyper_boundary: mix [S, S]");
+  if (outw.has_value()) TORCH_CHECK(outw->numel() == S && outw->is_contiguous(), "hyper_boundary: outw [S]");
+  if (inw.has_value()) TORCH_CHECK(inw->numel() == S && inw->is_contiguous(), "hyper_boundary: inw [S]");
+  if (h.has_value())
+    TORCH_CHECK(h->is_contiguous() && h->dim() == 2 && h->size(0) == T && h->size(1) == W && ln_w.has_value() && ln_w->numel() == W &&
+                    ln_w->is_contiguous() && (!ln_b.has_value() || (ln_b->numel() == W && ln_b->is_contiguous())),
+                "hyper_boundary: h [T, W] goes with ln_w [W] (and ln_b [W])");
+  auto opt = [](const c10::optional<Tensor>& t, const char* n) { return t.has_value() ? f32(*t, n) : nullptr; };
+  check(nrl_hyper_boundary(f32w(xs, "xs"), S, opt(o, "o"), opt(o_bias, "o_bias"), opt(self_w, "self_w"), opt(mix, "mix"), opt(outw, "outw"),
+                           opt(inw, "inw"), opt(ln_w, "ln_w"), opt(ln_b, "ln_b"), static_cast<float>(eps),
+                           h.has_value() ? h->data_ptr() : nullptr, h.has_value() ? typed(*h, "h") : 1, T, W, cur_stream()),
+        "hyper_boundary");
+}
+
+void mlstm_scan(const Tensor& qkv, int64_t col_q, int64_t col_k, int64_t col_v, int64_t col_i, int64_t col_f,
+                const c10::optional<Tensor>& i_bias, const c10::optional<Tensor>& f_bias, double cap, double q_scale, Tensor state,
+                Tensor mstate, Tensor o, Tensor m_out, const Tensor& cu, const Tensor& start, const Tensor& state_slot, int64_t impl) {
+  c10::cuda::CUDAGuard guard(qkv.device());
+  TORCH_CHECK(state.dim() == 4 && state.is_contiguous() && mstate.dim() == 2 && mstate.is_contiguous() && mstate.size(0) == state.size(0) &&
+                  mstate.size(1) == state.size(1), "mlstm_scan: state [slots, heads, D, >= Dv + 1], mstate [slots, heads]");
+  const int T = static_cast<int>(qkv.size(0)), heads = static_cast<int>(state.size(1)), D = static_cast<int>(state.size(2)),
+            Cs = static_cast<int>(state.size(3)), E = static_cast<int>(start.numel());
+  TORCH_CHECK(o.dim() == 2 && o.size(0) == T && o.size(1) % heads == 0, "mlstm_scan: o [T, heads * (Dv + 1)]");
+  const int Dv = static_cast<int>(o.size(1) / heads) - 1;
+  TORCH_CHECK(Dv >= 1 && Cs >= Dv + 1, "mlstm_scan: the state's rows hold at least Dv + 1 columns");
+  const int64_t wd = qkv.size(1);
+  TORCH_CHECK(qkv.dim() == 2 && Dv >= 1 && col_q >= 0 && col_q + heads * D <= wd && col_k >= 0 && col_k + heads * D <= wd && col_v >= 0 &&
+                  col_v + heads * Dv <= wd && col_i >= 0 && col_i + heads <= wd && col_f >= 0 && col_f + heads <= wd, "mlstm_scan: columns");
+  TORCH_CHECK(o.is_contiguous() && o.numel() == static_cast<int64_t>(T) * heads * (Dv + 1) && m_out.is_contiguous() &&
+                  m_out.numel() == static_cast<int64_t>(T) * heads && cu.numel() == E + 1 && state_slot.numel() == E, "mlstm_scan: outputs / plan");
+  if (i_bias.has_value()) TORCH_CHECK(i_bias->numel() == heads && i_bias->is_contiguous(), "mlstm_scan: i_bias [heads]");
+  if (f_bias.has_value()) TORCH_CHECK(f_bias->numel() == heads && f_bias->is_contiguous(), "mlstm_scan: f_bias [heads]");
+  check(nrl_mlstm_scan(f32(qkv, "qkv"), qkv.stride(0), static_cast<int>(col_q), static_cast<int>(col_k), static_cast<int>(col_v),
+                       static_cast<int>(col_i), static_cast<int>(col_f), i_bias.has_value() ? f32(*i_bias, "i_bias") : nullptr,
+                       f_bias.has_value() ? f32(*f_bias, "f_bias") : nullptr, static_cast<float>(cap), static_cast<float>(q_scale),
+                       f32w(state, "state"), f32w(mstate, "mstate"), f32w(o, "o"), f32w(m_out, "m_out"), i32(cu, "cu"), i32(start, "start"),
+                       i32(state_slot, "state_slot"), E, heads, D, Dv, Cs, T == E ? 1 : 0, static_cast<int>(impl), cur_stream()),
+        "mlstm_scan");
+}
+
+void mlstm_out(const Tensor& o, const Tensor& m, const Tensor& gate, const Tensor& w, double eps, double scale, Tensor out, int64_t heads) {
+  c10::cuda::CUDAGuard guard(o.device());
+  const int T = static_cast<int>(m.numel() / heads);
+  const int Dv = static_cast<int>(o.numel() / (static_cast<int64_t>(T > 0 ? T : 1) * heads)) - 1;
+  TORCH_CHECK(o.is_contiguous() && m.is_contiguous() && (T == 0 || o.numel() == static_cast<int64_t>(T) * heads * (Dv + 1)), "mlstm_out: o / m");
+  TORCH_CHECK(gate.dim() == 2 && gate.size(0) == T && gate.size(1) == heads * Dv && w.numel() == heads * Dv && w.is_contiguous() &&
+                  out.dim() == 2 && out.size(0) == T && out.size(1) == heads * Dv, "mlstm_out: gate / w / out [.., heads * Dv]");
+  check(nrl_mlstm_out(f32(o, "o"), f32(m, "m"), f32(gate, "gate"), gate.stride(0), f32(w, "w"), static_cast<float>(eps),
+                      static_cast<float>(scale), out.data_ptr(), out.stride(0), typed(out, "out"), T, static_cast<int>(heads), Dv, cur_stream()),
+        "mlstm_out");
+}
+
+void rot_kv_write(Tensor q, const c10::optional<Tensor>& q_bias, const c10::optional<Tensor>& k, const c10::optional<Tensor>& k_bias,
+                  const c10::optional<Tensor>& v, const c10::optional<Tensor>& freq, int64_t rdims, double mult, bool interleaved,
+                  bool unit_norm, const c10::optional<Tensor>& q_norm_w, const c10::optional<Tensor>& k_norm_w, double eps, const Tensor& pos,
+                  const Tensor& kv_slot, Tensor k_cache, Tensor v_cache) {
+  c10::cuda::CUDAGuard guard(q.device());
+  const int cf = typed(k_cache, "k_cache");
+  TORCH_CHECK(typed(v_cache, "v_cache") == cf && k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(),
+              "rot_kv_write: caches [pages, heads, page, size] of one type");
+  const int T = static_cast<int>(q.size(0)), Hk = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)),
+            D = static_cast<int>(k_cache.size(3)), Hv = static_cast<int>(v_cache.size(1)), Dv = static_cast<int>(v_cache.size(3));
+  TORCH_CHECK(q.dim() == 2 && q.size(1) % D == 0, "rot_kv_write: q [T, Hq * D]");
+  const int Hq = static_cast<int>(q.size(1)) / D;
+  if (k.has_value()) TORCH_CHECK(k->dim() == 2 && k->size(0) == T && k->size(1) == static_cast<int64_t>(Hk) * D, "rot_kv_write: k [T, Hk * D]");
+  if (v.has_value()) TORCH_CHECK(k.has_value() && v->dim() == 2 && v->size(0) == T && v->size(1) == static_cast<int64_t>(Hv) * Dv, "rot_kv_write: v [T, Hv * Dv]");
+  if (q_bias.has_value()) TORCH_CHECK(q_bias->numel() == static_cast<int64_t>(Hq) * D && q_bias->is_contiguous(), "rot_kv_write: q_bias");
+  if (k_bias.has_value()) TORCH_CHECK(k_bias->numel() == static_cast<int64_t>(Hk) * D && k_bias->is_contiguous(), "rot_kv_write: k_bias");
+  if (q_norm_w.has_value()) TORCH_CHECK(q_norm_w->numel() == D && q_norm_w->is_contiguous(), "rot_kv_write: q_norm_w [D]");
+  if (k_norm_w.has_value()) TORCH_CHECK(k_norm_w->numel() == D && k_norm_w->is_contiguous(), "rot_kv_write: k_norm_w [D]");
+  if (rdims > 0)
+    TORCH_CHECK(freq.has_value() && freq->is_cuda() && freq->scalar_type() == torch::kFloat64 && freq->is_contiguous() && freq->numel() == rdims / 2,
+                "rot_kv_write: freq double [rdims / 2]");
+  check(nrl_rot_kv_write(f32w(q, "q"), q.stride(0), q_bias.has_value() ? f32(*q_bias, "q_bias") : nullptr, k.has_value() ? f32(*k, "k") : nullptr,
+                         k.has_value() ? k->stride(0) : 0, k_bias.has_value() ? f32(*k_bias, "k_bias") : nullptr,
+                         v.has_value() ? f32(*v, "v") : nullptr, v.has_value() ? v->stride(0) : 0,
+                         rdims > 0 ? freq->data_ptr<double>() : nullptr, static_cast<int>(rdims), static_cast<float>(mult), interleaved ? 1 : 0,
+                         unit_norm ? 1 : 0, q_norm_w.has_value() ? f32(*q_norm_w, "q_norm_w") : nullptr,
+                         k_norm_w.has_value() ? f32(*k_norm_w, "k_norm_w") : nullptr, static_cast<float>(eps), i32(pos, "pos"),
+                         i32(kv_slot, "kv_slot"), k_cache.data_ptr(), v_cache.data_ptr(), cf, page, T, Hq, Hk, Hv, D, Dv, cur_stream()),
+        "rot_kv_write");
+}
+
+void diff_combine(const Tensor& a, double lambda, double post, double eps, const c10::optional<Tensor>& gate, double out_scale, Tensor out,
+                  int64_t heads, int64_t kv_heads) {
+  c10::cuda::CUDAGuard guard(a.device());
+  const int T = static_cast<int>(a.size(0));
+  TORCH_CHECK(a.dim() == 2 && out.dim() == 2 && out.size(0) == T && a.size(1) == 2 * out.size(1) && out.size(1) % heads == 0,
+              "diff_combine: a [T, 2 H Dv], out [T, H Dv]");
+  const int Dv = static_cast<int>(out.size(1) / heads);
+  if (gate.has_value()) TORCH_CHECK(gate->dim() == 2 && gate->size(0) == T && gate->size(1) == out.size(1), "diff_combine: gate [T, H Dv]");
+  check(nrl_diff_combine(a.data_ptr(), a.stride(0), typed(a, "a"), static_cast<float>(lambda), static_cast<float>(post), static_cast<float>(eps),
+                         gate.has_value() ? f32(*gate, "gate") : nullptr, gate.has_value() ? gate->stride(0) : 0, static_cast<float>(out_scale),
+                         out.data_ptr(), out.stride(0), typed(out, "out"), T, static_cast<int>(heads), static_cast<int>(kv_heads), Dv,
+                         cur_stream()),
+        "diff_combine");
 }
 
 void kv_write_blend(const Tensor& k, Tensor v, const c10::optional<Tensor>& v_other, const c10::optional<Tensor>& lambda, Tensor k_cache,
@@ -360,7 +491,7 @@ void swiglu_cols(const Tensor& in, const c10::optional<Tensor>& rgate, Tensor ou
 }
 
 void moe_route_all(const Tensor& router, const c10::optional<Tensor>& correction, int64_t n_real, int64_t top, double route_scale,
-                   const c10::optional<Tensor>& gu, int64_t ff, const c10::optional<Tensor>& act, const c10::optional<Tensor>& ids,
+                   int64_t groups, int64_t keep, const c10::optional<Tensor>& gu, int64_t ff, const c10::optional<Tensor>& act, const c10::optional<Tensor>& ids,
                    const c10::optional<Tensor>& wts, const c10::optional<Tensor>& self_w) {
   c10::cuda::CUDAGuard guard(router.device());
   TORCH_CHECK(router.dim() == 2, "moe_route_all: router [T, E]");
@@ -375,8 +506,8 @@ void moe_route_all(const Tensor& router, const c10::optional<Tensor>& correction
   if (self_w.has_value()) TORCH_CHECK(self_w->is_contiguous() && self_w->numel() == T, "moe_route_all: self_w float [T]");
   Tensor wt = wts.has_value() ? *wts : Tensor(), sw = self_w.has_value() ? *self_w : Tensor();
   check(nrl_moe_route_all(f32(router, "router"), router.stride(0), correction.has_value() ? f32(*correction, "correction") : nullptr, E,
-                          static_cast<int>(n_real), static_cast<int>(top), static_cast<float>(route_scale),
-                          gu.has_value() ? f32(*gu, "gu") : nullptr, gu.has_value() ? gu->stride(0) : 0, static_cast<int>(ff),
+                          static_cast<int>(n_real), static_cast<int>(top), static_cast<float>(route_scale), static_cast<int>(groups),
+                          static_cast<int>(keep), gu.has_value() ? f32(*gu, "gu") : nullptr, gu.has_value() ? gu->stride(0) : 0, static_cast<int>(ff),
                           act.has_value() ? act->data_ptr() : nullptr, act.has_value() ? act->stride(0) : 0,
                           act.has_value() ? typed(*act, "act") : 1, ids.has_value() ? ids->data_ptr<int>() : nullptr,
                           wts.has_value() ? f32w(wt, "wts") : nullptr, self_w.has_value() ? f32w(sw, "self_w") : nullptr, T, cur_stream()),
@@ -545,7 +676,14 @@ void bind_hybrid(pybind11::module_& m) {
         pybind11::arg("window"), pybind11::arg("scale"), pybind11::arg("out_scale"), pybind11::arg("out"), pybind11::arg("impl") = 0,
         pybind11::arg("chunked") = false, pybind11::arg("head_scale") = pybind11::none(), pybind11::arg("head_slope") = pybind11::none(),
         pybind11::arg("gate") = pybind11::none(), pybind11::arg("head_sink") = pybind11::none(), pybind11::arg("kv_shared") = false,
-        pybind11::arg("value_size") = 0, pybind11::arg("heads") = 0);
+        pybind11::arg("value_size") = 0, pybind11::arg("heads") = 0, pybind11::arg("softcap") = 0.0, pybind11::arg("keep_first") = 0,
+        pybind11::arg("dist_bias") = pybind11::none(), pybind11::arg("v_div") = 1);
+  m.def("embed_streams", &embed_streams, "xs[t, s] = embed[tok[t]] * scale for every residual stream");
+  m.def("hyper_boundary", &hyper_boundary, "close a sublayer over several mixed residual streams and layer-norm the next one's input");
+  m.def("mlstm_scan", &mlstm_scan, "matrix memory with exponential gates and a running maximum, state carried per slot");
+  m.def("mlstm_out", &mlstm_out, "normaliser division, per-head RMS norm, weight and sigmoid gate of the matrix memory's read-out");
+  m.def("rot_kv_write", &rot_kv_write, "biased, rotated, optionally unit-normed queries (in place) and keys (into pages); values into pages");
+  m.def("diff_combine", &diff_combine, "o = a1 - lambda a2 of two score maps, per-head RMS norm, gate");
   m.def("kv_write_blend", &kv_write_blend, "keys and (optionally blended) values of a step's tokens into their pages");
   m.def("embed_hashed", &embed_hashed, "x0 = embed[tok] * scale + pair[hash(previous token, token)] (float), previous tokens carried per slot");
   m.def("group_norm_residual", &group_norm_residual, "x += groupnorm(o * sigmoid(gate)) * w_post; h = groupnorm(x) * w_pre");

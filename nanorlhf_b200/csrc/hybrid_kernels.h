@@ -24,6 +24,12 @@ typedef struct {
   int kv_shared;             // 1: values are the first Dv columns of the key rows (v_cache == k_cache, rows of D): latent attention
   long q_head_stride;        // 0: head h of token t starts at q[t * sq + h * D]; else at q[t * sq + h * q_head_stride] (queries stored
                              // head-major, as a batched GEMM leaves them); scalar and latent kernels only
+  float softcap;             // > 0: score <- softcap * tanh(score / softcap), after the scale and before the terms below
+  int keep_first;            // > 0 (window form): keys at positions < keep_first stay visible however far back they lie
+  const float* dist_bias;    // [dist_max + 1, Hq] or null: dist_bias[min(p - j, dist_max), h] is added to the score (not scaled)
+  int dist_max;
+  int v_div;                 // > 1: key head g reads the values of head g / v_div of a value cache with Hkv / v_div heads (several
+                             // score maps over one set of values)
 } NrlAttnMods;
 
 extern "C" {
@@ -87,9 +93,11 @@ cudaError_t nrl_swiglu_cols(const float* in, long si, const float* rgate, long s
 // softmax + correction (correction [E] or null; ties: lowest index) are chosen; weight = softmax / (sum over the chosen + 1e-20)
 // * route_scale.  ids [T, top]; wts [T, top] (0 for a chosen identity expert); self_w [T] = summed weights of the chosen
 // identity experts (needed when n_real < E).  Dense form as nrl_moe_route, over the n_real experts.
+// groups > 1: the E outputs form `groups` equal groups of neighbours; a group's score is its largest choice score (score +
+// correction) and only experts of the `keep` best groups can be chosen (the others count as -inf; ties: the lower group).
 cudaError_t nrl_moe_route_all(const float* router, long sr, const float* correction, int E, int n_real, int top, float route_scale,
-                              const float* gu, long sgu, int ff, void* act, long sa, int act_f32, int* ids, float* wts, float* self_w,
-                              int T, cudaStream_t s);
+                              int groups, int keep, const float* gu, long sgu, int ff, void* act, long sa, int act_f32, int* ids,
+                              float* wts, float* self_w, int T, cudaStream_t s);
 
 // Layer boundary of a depth-weighted residual stream.  results: float [n_results_cap, stride_r] with rows of W.
 //   if (o)  results[i] = xprev + o                      (closes the previous layer)
@@ -208,4 +216,46 @@ cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cach
                                      int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
                                      void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
                                      const NrlAttnMods* mods, cudaStream_t s);
+// Several residual streams mixed by learned weights (hyper-connections), layer norms with weight and bias.  xs float [T, S, W].
+//   nrl_embed_streams:   xs[t, s] = embed[tok[t]] * scale for every stream s
+//   nrl_hyper_boundary:  if (o)  y = o + o_bias + self_w[t] * h[t]  (o float [T, W]; o_bias [W], self_w [T] or null; h still holds
+//                                the closing sublayer's input);  x_t <- sum_s mix[s, t] x_s + outw[t] y for all t at once
+//                                (mix [S, S] indexed [from, to], outw [S]; null: identity / ones)
+//                        if (h)  u = sum_s inw[s] x_s (inw null: the plain sum);  h (typed) = (u - mean) / sqrt(var + eps) * ln_w + ln_b
+cudaError_t nrl_embed_streams(const void* embed, int w_f32, const int* tok, float scale, float* xs, int T, int S, int W, cudaStream_t s);
+cudaError_t nrl_hyper_boundary(float* xs, int S, const float* o, const float* o_bias, const float* self_w, const float* mix,
+                               const float* outw, const float* inw, const float* ln_w, const float* ln_b, float eps, void* h, int h_f32,
+                               int T, int W, cudaStream_t s);
+
+// Matrix memory with exponential gates (mLSTM).  qkv float [T, *] (row stride sq): q at col_q, k at col_k (heads * D each), v at
+// col_v (heads * Dv), raw gates at col_i / col_f (heads each; i_bias / f_bias [heads] or null are added).
+//   i = cap tanh(raw_i / cap);  f = logsigmoid(cap tanh(raw_f / cap))  (cap <= 0: no cap);  m' = max(f + m, i)
+//   S = exp(f + m - m') S + exp(i - m') k [v, 1]^T      state float [slots, heads, D, Cs], Cs >= Dv + 1 (column Dv is the normaliser n;
+//                                                       rows padded to a multiple of 8 floats keep the accesses on sector borders)
+//   o [T, heads, Dv + 1] = S^T (q * q_scale)            mstate float [slots, heads] carries m (0 for a new sequence); m_out [T, heads]
+// `impl`: 0 picks by size, 1 a state column per thread in registers (D <= 128), 2 the state in global memory.  single_token: every
+// entry holds one token (two threads then share a column of a 128-row state).
+//   nrl_mlstm_out:  y = o[:Dv] / (max(|o[Dv]|, exp(-m)) + 1e-6);  out (typed) = scale * y / rms_head(y) * w * sigmoid(gate)
+//                   (gate float [T, heads * Dv], row stride sg; w [heads * Dv])
+cudaError_t nrl_mlstm_scan(const float* qkv, long sq, int col_q, int col_k, int col_v, int col_i, int col_f, const float* i_bias,
+                           const float* f_bias, float cap, float q_scale, float* state, float* mstate, float* o, float* m_out,
+                           const int* cu, const int* start, const int* state_slot, int E, int heads, int D, int Dv, int Cs,
+                           int single_token, int impl, cudaStream_t s);
+cudaError_t nrl_mlstm_out(const float* o, const float* m, const float* gate, long sg, const float* w, float eps, float scale, void* out,
+                          long so, int out_f32, int T, int heads, int Dv, cudaStream_t s);
+
+// Write side of rotated attention.  q float [T, Hq * D] (in place), k float [T, Hk * D], v float [T, Hv * Dv] or null (the values
+// are then the keys as projected, bias included: Hv == Hk, Dv == D); biases [heads * D] or null.  The first `rdims` columns of every
+// head turn by pos * freq[i] (freq double [rdims / 2]; cos and sin times mult; interleaved 1: pairs (2i, 2i + 1), 0: (i, i + rdims / 2));
+// unit_norm: q and k are then divided by their root mean square per head (eps inside the root; times q_norm_w / k_norm_w [D] when
+// given).  k == nullptr: queries only.  Caches typed [pages, heads, page, D or Dv].
+cudaError_t nrl_rot_kv_write(float* q, long sq, const float* q_bias, const float* k, long sk, const float* k_bias, const float* v, long sv,
+                             const double* freq, int rdims, float mult, int interleaved, int unit_norm, const float* q_norm_w,
+                             const float* k_norm_w, float eps, const int* pos, const int* kv_slot, void* k_cache, void* v_cache,
+                             int cache_f32, int page, int T, int Hq, int Hk, int Hv, int D, int Dv, cudaStream_t s);
+// Differential attention, read side.  a typed [T, 2 H, Dv] (row stride sa): outputs of the two score maps, heads ordered (key/value
+// head, map, query head of the group).  o = a_1 - lambda a_2;  out (typed, [T, H * Dv] in the order key/value head, query head)
+// = out_scale * post * o / rms_head(o) * sigmoid(gate)   (gate float [T, H * Dv], row stride sg, or null)
+cudaError_t nrl_diff_combine(const void* a, long sa, int a_f32, float lambda, float post, float eps, const float* gate, long sg,
+                             float out_scale, void* out, long so, int out_f32, int T, int H, int Hkv, int Dv, cudaStream_t s);
 }

@@ -3,6 +3,8 @@
 // every entry (a run of consecutive tokens of one sequence: a prompt portion or one decoded token) starts from the state
 // its slot holds (zero when the sequence is new) and leaves the updated state there.  All arithmetic is float.
 // Compiled WITHOUT fast-math.
+#include <cuda_bf16.h>
+
 #include "hybrid_kernels.h"
 
 namespace {
@@ -721,6 +723,183 @@ int pick_rows(int cols, int rows) {
   return R;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Matrix memory with exponential gates and a running maximum (mLSTM).  Per head, with log gates i and f of the token and the
+// carried maximum m (0 for a new sequence):  m' = max(f + m, i);  S = exp(f + m - m') S + exp(i - m') k v^T  and the
+// normaliser n likewise with k alone.  n is kept as one more column of the state (a value that is always 1), so the state
+// of a head is [D, Dv + 1] and its read-out S^T q gives the numerator in columns 0 .. Dv-1 and n . q in column Dv; the division
+// is left to nrl_mlstm_out.  The raw gates are capped (cap * tanh(z / cap), cap > 0) and the forget gate goes through
+// log-sigmoid.  Block per (entry, head): thread c keeps column c of the state in ROWS registers; one more warp forms the
+// gates of the next token while the columns work on the current one (the recurrence of m is one dependent chain per head).
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float logsigmoid_(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+struct MlstmGate {
+  float a, b, m;
+};
+__device__ __forceinline__ MlstmGate mlstm_gate(float i_raw, float f_raw, float cap, float m_prev) {
+  const float ig = cap > 0.f ? cap * tanhf(i_raw / cap) : i_raw;
+  const float fg = logsigmoid_(cap > 0.f ? cap * tanhf(f_raw / cap) : f_raw);
+  MlstmGate g;
+  g.m = fmaxf(fg + m_prev, ig);
+  g.a = expf(fg + m_prev - g.m);
+  g.b = expf(ig - g.m);
+  return g;
+}
+
+// SPLIT (1 or 2) threads share a column as in the other column-resident scans (ColStage): neighbouring lanes hold the upper and
+// the lower half of its rows and add their partial sums with one shuffle.
+template <int ROWS, int SPLIT>
+__global__ void __launch_bounds__(ROWS >= 128 ? 320 : ROWS >= 64 ? 256 : 544)      // 128 rows: 168 registers, two blocks of 192 threads per SM
+mlstm_scan_col_kernel(const float* __restrict__ qkv, long sq, int col_q, int col_k, int col_v, int col_i, int col_f,
+                      const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
+                      float* __restrict__ state, float* __restrict__ mstate, float* __restrict__ o, float* __restrict__ m_out,
+                      const int* __restrict__ cu, const int* __restrict__ start, const int* __restrict__ state_slot, int heads, int D,
+                      int Dv, int Cs) {
+  using St = ColStage<ROWS, SPLIT>;
+  constexpr int RH = St::RH, VL = St::VL, L = 2 * VL + 4;  // per token: q | k | a, b
+  constexpr int kStagePre = (2 * ROWS + 63) / 64;          // a block has at least 64 threads
+  __shared__ __align__(16) float stage[2 * L];
+  const int e = blockIdx.x, h = blockIdx.y;
+  const int tid = threadIdx.x, nth = blockDim.x, ncol = nth - 32, C = Dv + 1;        // ncol threads own columns, the last warp the gates
+  const int c = tid / SPLIT, half = tid % SPLIT, r0 = half * RH;
+  const bool gate_lane = tid == ncol, col_thread = tid < ncol, live = col_thread && c < C;
+  const long slot = state_slot[e];
+  float* gS = state + (slot * heads + h) * D * Cs;       // rows of Cs >= Dv + 1 floats
+  const bool carried = start[e] > 0;
+  float S[RH];
+#pragma unroll
+  for (int i = 0; i < RH; ++i) S[i] = (live && r0 + i < D && carried) ? gS[static_cast<long>(r0 + i) * Cs + c] : 0.f;
+  const int t0 = cu[e], t1 = cu[e + 1];
+  const float ib = i_bias != nullptr ? i_bias[h] : 0.f, fb = f_bias != nullptr ? f_bias[h] : 0.f;
+  float m_run = carried ? mstate[slot * heads + h] : 0.f;
+  MlstmGate gt = {0.f, 0.f, 0.f};
+  float pre[kStagePre], pre_v = 0.f;
+  auto fetch = [&](int t) {
+    const float* row = qkv + static_cast<long>(t) * sq;
+#pragma unroll
+    for (int i = 0; i < kStagePre; ++i) {
+      const int idx = tid + i * nth;
+      if (idx < 2 * ROWS) {
+        const int d = idx < ROWS ? idx : idx - ROWS;
+        pre[i] = d < D ? (idx < ROWS ? row[col_q + h * D + d] * q_scale : row[col_k + h * D + d]) : 0.f;
+      }
+    }
+    if (col_thread) pre_v = c < Dv ? row[col_v + h * Dv + c] : 1.f;
+    if (gate_lane) {
+      gt = mlstm_gate(row[col_i + h] + ib, row[col_f + h] + fb, cap, m_run);
+      m_run = gt.m;
+    }
+  };
+  if (t0 < t1) fetch(t0);
+  for (int t = t0; t < t1; ++t) {
+    float* v = stage + ((t - t0) & 1) * L;
+#pragma unroll
+    for (int i = 0; i < kStagePre; ++i) {
+      const int idx = tid + i * nth;
+      if (idx < 2 * ROWS) v[(idx < ROWS ? 0 : VL) + St::at(idx < ROWS ? idx : idx - ROWS)] = pre[i];
+    }
+    if (gate_lane) {
+      v[2 * VL] = gt.a;
+      v[2 * VL + 1] = gt.b;
+      m_out[static_cast<long>(t) * heads + h] = gt.m;
+    }
+    const float v_cur = pre_v;
+    __syncthreads();
+    if (t + 1 < t1) fetch(t + 1);
+    if (col_thread) {
+      const float a = v[2 * VL], bv = v[2 * VL + 1] * v_cur;
+      const float4* vq = reinterpret_cast<const float4*>(v + half * (RH + 4));
+      const float4* vk = reinterpret_cast<const float4*>(v + VL + half * (RH + 4));
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < RH / 4; ++i) {
+        const float4 kk = vk[i], qq = vq[i];
+        S[4 * i] = a * S[4 * i] + kk.x * bv;
+        S[4 * i + 1] = a * S[4 * i + 1] + kk.y * bv;
+        S[4 * i + 2] = a * S[4 * i + 2] + kk.z * bv;
+        S[4 * i + 3] = a * S[4 * i + 3] + kk.w * bv;
+        acc[0] += S[4 * i] * qq.x;
+        acc[1] += S[4 * i + 1] * qq.y;
+        acc[2] += S[4 * i + 2] * qq.z;
+        acc[3] += S[4 * i + 3] * qq.w;
+      }
+      float tot = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      if (SPLIT == 2) tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+      if (live && half == 0) o[(static_cast<long>(t) * heads + h) * C + c] = tot;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < RH; ++i)
+      if (r0 + i < D) gS[static_cast<long>(r0 + i) * Cs + c] = S[i];
+  }
+  if (gate_lane && t0 < t1) mstate[slot * heads + h] = m_run;
+}
+
+// Any size: the state stays in global memory, thread per column, every thread forms the gates itself.
+__global__ void mlstm_scan_kernel(const float* __restrict__ qkv, long sq, int col_q, int col_k, int col_v, int col_i, int col_f,
+                                  const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
+                                  float* __restrict__ state, float* __restrict__ mstate, float* __restrict__ o, float* __restrict__ m_out,
+                                  const int* __restrict__ cu, const int* __restrict__ start, const int* __restrict__ state_slot, int heads,
+                                  int D, int Dv, int Cs) {
+  const int e = blockIdx.x, h = blockIdx.y, C = Dv + 1;
+  const long slot = state_slot[e];
+  float* gS = state + (slot * heads + h) * D * Cs;
+  const bool carried = start[e] > 0;
+  const float ib = i_bias != nullptr ? i_bias[h] : 0.f, fb = f_bias != nullptr ? f_bias[h] : 0.f;
+  const float m0 = carried ? mstate[slot * heads + h] : 0.f;
+  __syncthreads();                                         // every thread has read the carried maximum before thread 0 replaces it
+  const int t0 = cu[e], t1 = cu[e + 1];
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float m_run = m0;
+    for (int t = t0; t < t1; ++t) {
+      const float* row = qkv + static_cast<long>(t) * sq;
+      const MlstmGate gt = mlstm_gate(row[col_i + h] + ib, row[col_f + h] + fb, cap, m_run);
+      m_run = gt.m;
+      const float bv = gt.b * (c < Dv ? row[col_v + h * Dv + c] : 1.f);
+      float acc = 0.f;
+      for (int d = 0; d < D; ++d) {
+        const float old = (carried || t > t0) ? gS[static_cast<long>(d) * Cs + c] : 0.f;
+        const float sv = gt.a * old + row[col_k + h * D + d] * bv;
+        gS[static_cast<long>(d) * Cs + c] = sv;
+        acc += sv * (row[col_q + h * D + d] * q_scale);
+      }
+      o[(static_cast<long>(t) * heads + h) * C + c] = acc;
+      if (c == 0) m_out[static_cast<long>(t) * heads + h] = gt.m;
+    }
+    if (c == 0 && t0 < t1) mstate[slot * heads + h] = m_run;
+  }
+}
+
+// warp per (token, head): y = o[:Dv] / (max(|o[Dv]|, exp(-m)) + 1e-6); out = scale * y / rms(y) * w * sigmoid(gate)
+template <typename OT>
+__global__ void mlstm_out_kernel(const float* __restrict__ o, const float* __restrict__ m, const float* __restrict__ gate, long sg,
+                                 const float* __restrict__ w, float eps, float scale, OT* __restrict__ out, long so, long T, int heads,
+                                 int Dv) {
+  const long wid = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= T * heads) return;
+  const long t = wid / heads;
+  const int h = static_cast<int>(wid - t * heads);
+  const float* row = o + wid * (Dv + 1);
+  const float inv = 1.f / (fmaxf(fabsf(row[Dv]), expf(-m[wid])) + 1e-6f);
+  float ss = 0.f;
+  for (int c = lane; c < Dv; c += 32) {
+    const float y = row[c] * inv;
+    ss += y * y;
+  }
+  ss = warp_sum(ss);
+  const float r = 1.f / sqrtf(ss / static_cast<float>(Dv) + eps);
+  for (int c = lane; c < Dv; c += 32) {
+    const long col = static_cast<long>(h) * Dv + c;
+    const float g = gate[t * sg + col];
+    const float val = scale * (row[c] * inv * r * w[col] * (1.f / (1.f + expf(-g))));
+    if constexpr (sizeof(OT) == 4) out[t * so + col] = val;
+    else out[t * so + col] = __float2bfloat16_rn(val);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -867,6 +1046,46 @@ cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, cons
   }
   delta_scan_kernel<<<dim3(E, heads), threads, smem, s>>>(qkv, sq, col_k, col_v, beta, decay, state, o, cu, start, state_slot, heads,
                                                           kv_heads, D, Dv, per_channel, R);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_mlstm_scan(const float* qkv, long sq, int col_q, int col_k, int col_v, int col_i, int col_f, const float* i_bias,
+                           const float* f_bias, float cap, float q_scale, float* state, float* mstate, float* o, float* m_out,
+                           const int* cu, const int* start, const int* state_slot, int E, int heads, int D, int Dv, int Cs,
+                           int single_token, int impl, cudaStream_t s) {
+  if (E <= 0) return cudaSuccess;
+  if (D < 1 || Dv < 1 || Cs < Dv + 1 || impl < 0 || impl > 2) return cudaErrorInvalidValue;
+  // Steps of single tokens only move the state: two threads per column of a 128-row state put more loads in flight.  Entries
+  // that hold runs of tokens are bound by the token loop, where one thread per column keeps its rows in registers without spills.
+  const int rt = D <= 16 ? 16 : D <= 32 ? 32 : D <= 64 ? 64 : 128;
+  const int split = single_token && rt == 128 && (((Dv + 1) * 2 + 31) / 32) * 32 + 32 <= 320 ? 2 : 1;
+  const int ncol = (((Dv + 1) * split + 31) / 32) * 32;
+  if (impl != 2 && D <= 128 && ncol + 32 <= (rt >= 128 ? 320 : rt >= 64 ? 256 : 544)) {
+#define NRL_ML(R_, S_)                                                                                                             \
+  mlstm_scan_col_kernel<R_, S_><<<dim3(E, heads), ncol + 32, 0, s>>>(qkv, sq, col_q, col_k, col_v, col_i, col_f, i_bias, f_bias, cap,  \
+                                                                     q_scale, state, mstate, o, m_out, cu, start, state_slot, heads, D, Dv, Cs)
+    if (rt == 16) NRL_ML(16, 1);
+    else if (rt == 32) NRL_ML(32, 1);
+    else if (rt == 64) NRL_ML(64, 1);
+    else if (split == 2) NRL_ML(128, 2);
+    else NRL_ML(128, 1);
+#undef NRL_ML
+    return cudaGetLastError();
+  }
+  if (impl == 1) return cudaErrorInvalidValue;
+  const int th = Dv + 1 >= 256 ? 256 : ((Dv + 1 + 31) / 32) * 32;
+  mlstm_scan_kernel<<<dim3(E, heads), th, 0, s>>>(qkv, sq, col_q, col_k, col_v, col_i, col_f, i_bias, f_bias, cap, q_scale, state, mstate,
+                                                  o, m_out, cu, start, state_slot, heads, D, Dv, Cs);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_mlstm_out(const float* o, const float* m, const float* gate, long sg, const float* w, float eps, float scale, void* out,
+                          long so, int out_f32, int T, int heads, int Dv, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  const long warps = static_cast<long>(T) * heads;
+  const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
+  if (out_f32) mlstm_out_kernel<float><<<blocks, 128, 0, s>>>(o, m, gate, sg, w, eps, scale, static_cast<float*>(out), so, T, heads, Dv);
+  else mlstm_out_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(o, m, gate, sg, w, eps, scale, static_cast<__nv_bfloat16*>(out), so, T, heads, Dv);
   return cudaGetLastError();
 }
 

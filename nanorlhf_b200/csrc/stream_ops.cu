@@ -472,8 +472,9 @@ __global__ void swiglu_cols_vec4_kernel(const float* __restrict__ in, long si, c
 //   act != nullptr (dense form):  act[t, e*ff + c] = weight_e * silu(gu[t, e*2ff + c]) * gu[t, e*2ff + ff + c] for e < n_real, 0 if not chosen
 template <typename OT>
 __global__ void moe_route_all_kernel(const float* __restrict__ router, long sr, const float* __restrict__ correction, int E, int n_real,
-                                     int top, float route_scale, const float* __restrict__ gu, long sgu, int ff, OT* __restrict__ act,
-                                     long sa, int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ self_w) {
+                                     int top, float route_scale, int groups, int keep, const float* __restrict__ gu, long sgu, int ff,
+                                     OT* __restrict__ act, long sa, int* __restrict__ ids, float* __restrict__ wts,
+                                     float* __restrict__ self_w) {
   extern __shared__ float smf[];
   float* sc = smf;                // [E] softmax scores
   float* ch = sc + E;             // [E] choice scores, -inf once taken
@@ -500,6 +501,34 @@ __global__ void moe_route_all_kernel(const float* __restrict__ router, long sr, 
       wsel[e] = 0.f;
     }
     __syncwarp();
+    if (groups > 1 && keep < groups) {
+      // Only the `keep` groups of neighbours with the largest choice score stay eligible (ties: the lower group).  A group is
+      // dropped when at least `keep` others come before it; its experts count as -inf.  Every lane walks the same groups.
+      const int gsz = E / groups;
+      for (int g = lane; g < groups; g += 32) {
+        float b = -INFINITY;
+        for (int e = g * gsz; e < (g + 1) * gsz; ++e) b = fmaxf(b, ch[e]);
+        wsel[g] = b;                                          // borrowed: groups <= E
+      }
+      __syncwarp();
+      unsigned drop = 0u;                                     // bit i: group lane + 32 i is dropped (groups <= 1024)
+      for (int g = lane, i = 0; g < groups; g += 32, ++i) {
+        const float mine = wsel[g];
+        int before = 0;
+        for (int o = 0; o < groups; ++o) {
+          const float v = wsel[o];
+          before += (v > mine || (v == mine && o < g)) ? 1 : 0;
+        }
+        if (before >= keep) drop |= 1u << i;
+      }
+      __syncwarp();
+      for (int g = lane, i = 0; g < groups; g += 32, ++i) {
+        wsel[g] = 0.f;
+        if (drop >> i & 1u)
+          for (int e = g * gsz; e < (g + 1) * gsz; ++e) ch[e] = -INFINITY;
+      }
+      __syncwarp();
+    }
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
       float best = -INFINITY;
@@ -694,6 +723,127 @@ cudaError_t launch_gated_norm(const float* y, long sy, const float* gate, long s
 
 namespace {
 inline bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
+// ---------------------------------------------------------------------------------------------------------------------
+// Several residual streams mixed by learned weights (hyper-connections), with a layer norm (weight and bias) in front of every
+// sublayer.  xs float [T, S, W].
+// ---------------------------------------------------------------------------------------------------------------------
+// xs[t, s, :] = embed[tok[t]] * scale for every stream s
+template <typename WT>
+__global__ void embed_streams_kernel(const WT* __restrict__ embed, const int* __restrict__ tok, float scale, float* __restrict__ xs,
+                                     int S, int W) {
+  const long t = blockIdx.x;
+  const WT* row = embed + static_cast<long>(tok[t]) * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = ld(row, c) * scale;
+    for (int s = 0; s < S; ++s) xs[(t * S + s) * W + c] = v;
+  }
+}
+
+constexpr int kMaxStreams = 8;
+
+// Block per token.  Closes a sublayer whose result is o (+ o_bias + self_w[t] * h, h being the sublayer's own input, still in
+// place) -- x_t <- sum_s mix[s, t] x_s + outw[t] y, all streams from the old ones -- and opens the next one:
+// u = sum_s inw[s] x_s (inw null: the plain sum), h = (u - mean) / sqrt(var + eps) * ln_w + ln_b.
+// SM: the stream count rounded up (loops are unrolled over it); V: columns per access (4 needs W % 4 == 0 and aligned rows).
+template <typename HT, int SM, int V>
+__global__ void hyper_boundary_kernel(float* __restrict__ xs, int S, const float* __restrict__ o, const float* __restrict__ o_bias,
+                                      const float* __restrict__ self_w, const float* __restrict__ mix, const float* __restrict__ outw,
+                                      const float* __restrict__ inw, const float* __restrict__ ln_w, const float* __restrict__ ln_b,
+                                      float eps, HT* __restrict__ h, int W) {
+  extern __shared__ __align__(16) float rowbuf[];       // [W]: u
+  __shared__ float red[32];
+  __shared__ float smix[kMaxStreams * kMaxStreams], sout[kMaxStreams], sin_[kMaxStreams];
+  const long t = blockIdx.x;
+  if (threadIdx.x < S * S) smix[threadIdx.x] = (o != nullptr && mix != nullptr) ? mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.f : 0.f);
+  if (threadIdx.x < S) {
+    sout[threadIdx.x] = (o != nullptr && outw != nullptr) ? outw[threadIdx.x] : 1.f;
+    sin_[threadIdx.x] = inw != nullptr ? inw[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  const float sw = (o != nullptr && self_w != nullptr) ? self_w[t] : 0.f;
+  float* xt = xs + t * S * W;
+  float sum = 0.f;
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    float xv[SM][V], u[V];
+#pragma unroll
+    for (int s = 0; s < SM; ++s)
+      if (s < S) ldv<V>(xt + static_cast<long>(s) * W + c, xv[s]);
+#pragma unroll
+    for (int e = 0; e < V; ++e) u[e] = 0.f;
+    if (o != nullptr) {
+      float y[V];
+      ldv<V>(o + t * W + c, y);
+      if (o_bias != nullptr) {
+        float b[V];
+        ldv<V>(o_bias + c, b);
+#pragma unroll
+        for (int e = 0; e < V; ++e) y[e] += b[e];
+      }
+      if (self_w != nullptr) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) y[e] += sw * ld(h, t * W + c + e);
+      }
+#pragma unroll
+      for (int to = 0; to < SM; ++to) {
+        if (to < S) {
+          float a[V];
+#pragma unroll
+          for (int e = 0; e < V; ++e) a[e] = 0.f;
+#pragma unroll
+          for (int s = 0; s < SM; ++s) {
+            if (s < S) {
+              const float m = smix[s * S + to];
+#pragma unroll
+              for (int e = 0; e < V; ++e) a[e] += m * xv[s][e];
+            }
+          }
+          const float ow = sout[to], iw = sin_[to];
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            a[e] += ow * y[e];
+            u[e] += iw * a[e];
+          }
+          stv<V>(xt + static_cast<long>(to) * W + c, a);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int s = 0; s < SM; ++s) {
+        if (s < S) {
+          const float iw = sin_[s];
+#pragma unroll
+          for (int e = 0; e < V; ++e) u[e] += iw * xv[s][e];
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      rowbuf[c + e] = u[e];
+      sum += u[e];
+    }
+  }
+  if (h == nullptr) return;
+  const float inv = 1.f / static_cast<float>(W);
+  const float mean = block_sum(sum, red) * inv;
+  float ss = 0.f;
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {     // a thread re-reads the columns it staged itself
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const float d = rowbuf[c + e] - mean;
+      ss += d * d;
+    }
+  }
+  const float r = 1.f / sqrtf(block_sum(ss, red) * inv + eps);
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    float hv[V], wv[V], bv[V];
+    ldv<V>(ln_w + c, wv);
+    if (ln_b != nullptr) ldv<V>(ln_b + c, bv);
+#pragma unroll
+    for (int e = 0; e < V; ++e) hv[e] = (rowbuf[c + e] - mean) * r * wv[e] + (ln_b != nullptr ? bv[e] : 0.f);
+    stv<V>(h + t * W + c, hv);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -845,19 +995,20 @@ cudaError_t nrl_swiglu_cols(const float* in, long si, const float* rgate, long s
 }
 
 cudaError_t nrl_moe_route_all(const float* router, long sr, const float* correction, int E, int n_real, int top, float route_scale,
-                              const float* gu, long sgu, int ff, void* act, long sa, int act_f32, int* ids, float* wts, float* self_w,
-                              int T, cudaStream_t s) {
+                              int groups, int keep, const float* gu, long sgu, int ff, void* act, long sa, int act_f32, int* ids,
+                              float* wts, float* self_w, int T, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
   if (E < 1 || top < 1 || top > E || top > 64 || E > 4096 || n_real < 0 || n_real > E || (n_real < E && self_w == nullptr))
     return cudaErrorInvalidValue;
+  if (groups > 1 && (E % groups != 0 || keep < 1 || groups > 1024 || keep * (E / groups) < top)) return cudaErrorInvalidValue;
   const size_t smem = sizeof(float) * 3 * E;
   const int th = act == nullptr ? 32 : 256;
   if (act_f32)
-    moe_route_all_kernel<float><<<T, th, smem, s>>>(router, sr, correction, E, n_real, top, route_scale, gu, sgu, ff,
+    moe_route_all_kernel<float><<<T, th, smem, s>>>(router, sr, correction, E, n_real, top, route_scale, groups, keep, gu, sgu, ff,
                                                     static_cast<float*>(act), sa, ids, wts, self_w);
   else
-    moe_route_all_kernel<__nv_bfloat16><<<T, th, smem, s>>>(router, sr, correction, E, n_real, top, route_scale, gu, sgu, ff,
-                                                            static_cast<__nv_bfloat16*>(act), sa, ids, wts, self_w);
+    moe_route_all_kernel<__nv_bfloat16><<<T, th, smem, s>>>(router, sr, correction, E, n_real, top, route_scale, groups, keep, gu, sgu,
+                                                            ff, static_cast<__nv_bfloat16*>(act), sa, ids, wts, self_w);
   return cudaGetLastError();
 }
 
@@ -919,6 +1070,47 @@ cudaError_t nrl_gated_part_rmsnorm(const float* y, long sy, const float* gate, l
   if (vec) NRL_GN(__nv_bfloat16, 4);
   NRL_GN(__nv_bfloat16, 1);
 #undef NRL_GN
+}
+
+cudaError_t nrl_embed_streams(const void* embed, int w_f32, const int* tok, float scale, float* xs, int T, int S, int W, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (S < 1) return cudaErrorInvalidValue;
+  const int th = W >= 512 ? 256 : 128;
+  if (w_f32) embed_streams_kernel<float><<<T, th, 0, s>>>(static_cast<const float*>(embed), tok, scale, xs, S, W);
+  else embed_streams_kernel<__nv_bfloat16><<<T, th, 0, s>>>(static_cast<const __nv_bfloat16*>(embed), tok, scale, xs, S, W);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_hyper_boundary(float* xs, int S, const float* o, const float* o_bias, const float* self_w, const float* mix,
+                               const float* outw, const float* inw, const float* ln_w, const float* ln_b, float eps, void* h, int h_f32,
+                               int T, int W, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (S < 1 || S > kMaxStreams || (h != nullptr && ln_w == nullptr) || (self_w != nullptr && h == nullptr)) return cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * W;
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  const bool vec = W % 4 == 0 && aligned(xs, 16) && (o == nullptr || aligned(o, 16)) && (o_bias == nullptr || aligned(o_bias, 16)) &&
+                   (h == nullptr || aligned(h, h_f32 ? 16 : 8)) && (ln_w == nullptr || aligned(ln_w, 16)) &&
+                   (ln_b == nullptr || aligned(ln_b, 16));
+  const int th = W >= 1024 * (vec ? 4 : 1) ? 256 : 128;
+#define NRL_HB(HT_, SM_, V_)                                                                                                       \
+  hyper_boundary_kernel<HT_, SM_, V_><<<T, th, smem, s>>>(xs, S, o, o_bias, self_w, mix, outw, inw, ln_w, ln_b, eps, static_cast<HT_*>(h), W)
+#define NRL_HB_S(HT_, V_)                                                                                                          \
+  do {                                                                                                                             \
+    if (S == 1) NRL_HB(HT_, 1, V_);                                                                                                \
+    else if (S == 2) NRL_HB(HT_, 2, V_);                                                                                           \
+    else if (S <= 4) NRL_HB(HT_, 4, V_);                                                                                           \
+    else NRL_HB(HT_, 8, V_);                                                                                                       \
+  } while (0)
+  if (h_f32) {
+    if (vec) NRL_HB_S(float, 4);
+    else NRL_HB_S(float, 1);
+  } else {
+    if (vec) NRL_HB_S(__nv_bfloat16, 4);
+    else NRL_HB_S(__nv_bfloat16, 1);
+  }
+#undef NRL_HB_S
+#undef NRL_HB
+  return cudaGetLastError();
 }
 
 }  // extern "C"

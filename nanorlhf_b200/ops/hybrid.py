@@ -76,18 +76,22 @@ WINDOW_IMPLS = {"auto": 0, "tile": 1, "simple": 2, "mma": 3}
 
 
 def window_attention(q, k_cache, v_cache, plan, window, scale, out_scale, out, impl: str = "auto", chunked: bool = False,
-                     head_scale=None, head_slope=None, gate=None, head_sink=None, value_size: int = 0):
+                     head_scale=None, head_slope=None, gate=None, head_sink=None, value_size: int = 0, softcap: float = 0.0,
+                     keep_first: int = 0, dist_bias=None, v_div: int = 1):
     """``impl``: "auto" (tensor cores for prompt portions over bf16 pages, the scalar tile kernel otherwise) or one kernel by
     name; a kernel that does not fit the shapes raises.  ``chunked``: keys of the query's own chunk of ``window`` positions
     instead of the last ``window`` keys.  ``head_scale`` / ``head_slope`` [heads]: per-head score multiplier and linear distance
     penalty; ``gate`` [T, heads]: the head's output is multiplied by sigmoid(gate); ``head_sink`` [heads]: the softmax denominator
     also holds exp(sink).  ``value_size`` > 0 (with ``v_cache is k_cache``): the values are the first ``value_size`` columns of the
     key rows (latent attention: one cached row per token serves as key and value of every head); ``q`` may then be head-major
-    [heads, T, >= D], the layout a batched GEMM leaves."""
+    [heads, T, >= D], the layout a batched GEMM leaves.  ``softcap`` > 0: the scaled score becomes softcap * tanh(score / softcap);
+    ``keep_first`` > 0: the first positions of a sequence stay visible behind the window; ``dist_bias`` [distances, heads]: row
+    min(distance, distances - 1) is added to the score (after scale and cap); ``v_div`` > 1: that many neighbouring key heads read
+    one value head (several score maps over the same values)."""
     native._count()
     _ext().window_attention(q, k_cache, v_cache, plan.block_table, plan.tok_entry, plan.pos, window, scale, out_scale, out,
                             WINDOW_IMPLS[impl], chunked, head_scale, head_slope, gate, head_sink, value_size > 0, value_size,
-                            q.shape[0] if q.dim() == 3 else 0)
+                            q.shape[0] if q.dim() == 3 else 0, softcap, keep_first, dist_bias, v_div)
 
 
 def kv_write_blend(k, v, v_other, lam, k_cache, v_cache, plan):
@@ -177,11 +181,13 @@ def swiglu_cols(gu, row_gate, out):
     _ext().swiglu_cols(gu, row_gate, out)
 
 
-def moe_route_all(router, correction, n_real, top, scale, gu=None, ff=0, act=None, ids=None, wts=None, self_w=None):
+def moe_route_all(router, correction, n_real, top, scale, gu=None, ff=0, act=None, ids=None, wts=None, self_w=None, groups: int = 1,
+                  keep: int = 1):
     """Routing by a softmax over all router outputs (the last ``E - n_real`` are identity experts), choice by score + correction,
-    weights = chosen scores / their sum * scale; ``self_w`` [T] receives the identity experts' weights."""
+    weights = chosen scores / their sum * scale; ``self_w`` [T] receives the identity experts' weights.  ``groups`` > 1: the outputs
+    form that many equal groups of neighbours and only the ``keep`` groups with the largest choice score can be chosen from."""
     native._count()
-    _ext().moe_route_all(router, correction, n_real, top, scale, gu, ff, act, ids, wts, self_w)
+    _ext().moe_route_all(router, correction, n_real, top, scale, groups, keep, gu, ff, act, ids, wts, self_w)
 
 
 def gla_prep(qkv, a_raw, a_bias, tau, decay, heads, dim):
@@ -217,3 +223,68 @@ def rotary_frequencies(dims: int, base: float, scaling=None):
         ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
         out.append(fi / factor * ramp + fi * (1.0 - ramp))
     return out, 0.1 * math.log(factor) + 1.0
+
+
+def embed_streams(embed, tok, scale, xs):
+    """xs[t, s] = embed[tok[t]] * scale for every residual stream s (xs float [T, S, W])."""
+    native._count()
+    _ext().embed_streams(embed, tok, scale, xs)
+
+
+def hyper_boundary(xs, o, o_bias, self_w, mix, outw, inw, ln_w, ln_b, eps, h):
+    """Boundary between sublayers over several mixed residual streams.  With ``o`` (the closing sublayer's result, plus ``o_bias`` [W]
+    and ``self_w[t] * h[t]``, h still being that sublayer's input): ``x_t <- sum_s mix[s, t] x_s + outw[t] y`` for all streams at once.
+    With ``h``: ``u = sum_s inw[s] x_s`` (``inw`` None: the plain sum) and ``h = layernorm(u) * ln_w + ln_b`` in the operand type."""
+    native._count()
+    _ext().hyper_boundary(xs, o, o_bias, self_w, mix, outw, inw, ln_w, ln_b, eps, h)
+
+
+MLSTM_IMPLS = {"auto": 0, "column": 1, "global": 2}
+
+
+def mlstm_scan(qkv, col_q, col_k, col_v, col_i, col_f, i_bias, f_bias, cap, q_scale, state, mstate, o, m_out, plan, impl: str = "auto"):
+    """Matrix memory with exponential gates: ``state`` [slots, heads, D, >= Dv + 1] holds S and, as column Dv, the normaliser n;
+    ``mstate`` [slots, heads] the running maximum.  ``o`` [T, heads, Dv + 1] receives S^T q (numerator | n . q), ``m_out`` [T, heads]
+    the maximum after every token."""
+    native._count()
+    _ext().mlstm_scan(qkv, col_q, col_k, col_v, col_i, col_f, i_bias, f_bias, cap, q_scale, state, mstate, o, m_out, plan.cu, plan.start,
+                      plan.state_slot, MLSTM_IMPLS[impl])
+
+
+def mlstm_out(o, m, gate, w, eps, scale, out, heads):
+    """y = o[:Dv] / (max(|o[Dv]|, exp(-m)) + 1e-6); out = scale * y / rms_head(y) * w * sigmoid(gate)."""
+    native._count()
+    _ext().mlstm_out(o, m, gate, w, eps, scale, out, heads)
+
+
+def rot_kv_write(q, q_bias, k, k_bias, v, freq, rot_dims, mult, interleaved, unit_norm, q_norm_w, k_norm_w, eps, plan, k_cache, v_cache):
+    """Biased, rotated and (``unit_norm``) RMS-normed queries in place and keys into their pages; values into their pages (``v`` None:
+    the values are the keys as projected).  ``k`` None: queries only."""
+    native._count()
+    _ext().rot_kv_write(q, q_bias, k, k_bias, v, freq, rot_dims, mult, interleaved, unit_norm, q_norm_w, k_norm_w, eps, plan.pos,
+                        plan.kv_slot, k_cache, v_cache)
+
+
+def diff_combine(a, lam, post, eps, gate, out_scale, out, heads, kv_heads):
+    """Two score maps over the same values: o = a_1 - lam a_2 per head, RMS-normed, times ``post`` and sigmoid(gate)."""
+    native._count()
+    _ext().diff_combine(a, lam, post, eps, gate, out_scale, out, heads, kv_heads)
+
+
+def distance_bias_table(rel, bias_max: int):
+    """Expand a bucketed distance bias ``rel`` [B, heads] into one row per distance 0 .. bias_max: the first B / 2 buckets hold one
+    distance each, the others grow logarithmically up to ``bias_max``, from where on the last bucket holds."""
+    import math
+
+    import torch
+    B = rel.shape[0]
+    half = B // 2
+    rows = []
+    for n in range(bias_max + 1):
+        if n < half:
+            rows.append(n)
+        elif bias_max <= half:
+            rows.append(B - 1)
+        else:
+            rows.append(min(B - 1, half + int(math.floor(math.log(n / half) / math.log(bias_max / half) * (B - half)))))
+    return rel.float()[torch.tensor(rows, device=rel.device)].contiguous()
