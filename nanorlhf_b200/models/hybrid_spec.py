@@ -19,8 +19,8 @@ from .hf_io import load_state_dict, save_state_dict
 
 @dataclass
 class MixerSpec:
-    """One token mixer of a layer.  ``kind``: window_attention | conv_attention | ssd | gated_delta | latent_attention | gla.
-    ``prefix``: tensor-name prefix."""
+    """One token mixer of a layer.  ``kind``: window_attention | conv_attention | ssd | gated_delta | latent_attention | gla |
+    rot_attention | mlstm.  ``prefix``: tensor-name prefix."""
     kind: str
     prefix: str
     out_scale: float = 1.0
@@ -52,6 +52,26 @@ class MixerSpec:
     head_sink: bool = False      # the softmax denominator also holds exp(sink_h) (tensor "sink"): a score with no key and no value
     # gla (gated linear attention, S = diag(decay) S + k v^T, o = S^T q D^-1/2; decay = sigmoid(a2 (a1 h) + a2.b)^(1 / tau) per key channel):
     tau: float = 1.0
+    # rot_attention (projections q / k / v with grouped heads; the first `rot_dims` columns of every head rotated (`rot_base`, `rot_layout`,
+    # `rot_scaling`; 0: no rotation); `window` keys seen (0: all earlier ones); `head_sink` as above; and the optional terms below):
+    qk_bias: bool = False        # biases on the q and k projections (tensors "q.b", "k.b")
+    out_bias: bool = False       # bias on the output projection (tensor "o.b")
+    unit_qk_norm: bool = False   # q and k divided by their root mean square per head after the rotation (no weight)
+    values_from_keys: bool = False   # no v projection: the values are the keys as projected (bias included), before rotation and norm
+    softcap: float = 0.0         # > 0: score <- softcap * tanh(score / softcap)
+    keep_first: int = 0          # > 0: the first positions of a sequence stay visible behind the window
+    bias_max: int = 0            # > 0: a learned bias per (distance bucket, head) is added to the score (tensor "rel" [buckets, heads]);
+                                 # the first half of the buckets hold one distance each, the others grow logarithmically up to bias_max
+    maps: int = 1                # 2: differential attention, q and k hold two score maps per head over the same values (tensors lq1, lk1,
+                                 # lq2, lk2 [dim]): o = a_1 - lambda a_2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, RMS-normed per
+                                 # head, times (1 - diff)
+    diff: float = 0.0
+    out_gate: bool = False       # the concatenated heads times sigmoid(g h), element by element (tensor "g" [heads * vdim, W])
+    kv_from: int = -1            # >= 0: no k / v projections; the layer reads the pages of that earlier layer
+    # mlstm (matrix memory with exponential gates: log gates i = cap tanh((i h + i.b) / cap), f = logsigmoid(cap tanh((f h + f.b) / cap));
+    # m' = max(f + m, i); S = exp(f + m - m') S + exp(i - m') k v^T, n likewise with k; o = S^T q / (max(|n . q|, exp(-m')) + 1e-6) with
+    # q scaled by dim^-1/2; per-head RMS norm, weight "norm", sigmoid gate "g"):
+    gate_cap: float = 0.0
 
 
 @dataclass
@@ -67,6 +87,8 @@ class LayerSpec:
                                  # "softmax_all": scores = softmax over all router outputs, chosen by score + "correction",
                                  #                weights = the chosen scores / their sum * route_scale
     route_scale: float = 1.0
+    route_groups: int = 1        # "softmax_all": > 1: the router outputs form that many equal groups of neighbours and only experts of the
+    route_keep: int = 1          # `route_keep` groups with the largest choice score can be chosen
     identity_experts: int = 0    # router outputs behind the `experts` real ones whose expert returns its input
     shared_ff: int = 0           # > 0: a SwiGLU expert of this width for every token (tensors "shared.*")
     shared_gate: bool = False    # its result times sigmoid(shared.sg h), one number per token
@@ -84,7 +106,10 @@ class StreamSpec:
     ``x += norm2b(g2 * ff(norm2 x))`` with group RMS norms (a weight per column) and, when ``gated_residual``, sigmoid gates
     ``g = sigmoid(rg h + rg.b)`` of the sublayer's input.  ``kind`` "post_norm": sublayers read the stream itself and only their
     result is normed, ``x += norm1(mixer(x))`` then ``x += norm2(ff(x))`` (single-group RMS norms with a weight per column); the
-    embedding is normed too (tensor "embed.norm")."""
+    embedding is normed too (tensor "embed.norm").  ``kind`` "hyper": ``streams`` copies of the stream (all equal to the embedding at
+    the start); sublayer q of a layer reads ``layernorm(sum_s hc<q>.in[s] x_s)`` (weight norm<q>, bias norm<q>.b) and every stream becomes
+    ``x_t <- sum_s hc<q>.mix[s, t] x_s + hc<q>.out[t] y``; the output reads the layer norm of the streams' sum (``hyper_weights`` False:
+    one stream with the plain residual sum, no hc tensors)."""
     kind: str = "depth_weighted"
     norm_groups: int = 1
     gated_residual: bool = False
@@ -94,6 +119,9 @@ class StreamSpec:
     pair_mul_prev: int = 0
     pair_mul_cur: int = 0
     logit_scale: float = 1.0
+    streams: int = 1                            # "hyper": copies of the residual stream
+    hyper_weights: bool = True                  # "hyper": the layers carry hc1 / hc2 tensors
+    tied_head: bool = False                     # logits = embed x (the table itself, without embed_scale); no "head" tensor
 
 
 def _mangle(name: str) -> str:

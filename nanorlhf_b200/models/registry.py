@@ -12,7 +12,8 @@ from typing import Callable, Dict, Tuple
 
 _REGISTRY: Dict[str, Tuple[type, str]] = {}
 _LAZY = {"Qwen2ForCausalLM": "qwen2", "qwen2": "qwen2", "Nezavik": "nezavik", "nezavik": "nezavik",
-         "Vilosun": "vilosun", "vilosun": "vilosun", "Damilix": "damilix", "damilix": "damilix"}
+         "Vilosun": "vilosun", "vilosun": "vilosun", "Damilix": "damilix", "damilix": "damilix",
+         "Lukarax": "lukarax", "lukarax": "lukarax"}
 
 
 def register_model(*names: str, sampler: str = "native") -> Callable[[type], type]:

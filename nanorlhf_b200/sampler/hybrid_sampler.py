@@ -21,6 +21,11 @@ step in a per-sequence slot) and it gives chunked prefill and continuous batchin
   layers may end with a gated per-layer token input (a third stage); its mixers are latent attention (one cached latent row
   per token serves all heads: queries are absorbed into the latent space before the paged attention kernel and the result
   is expanded per head after it) and gated linear attention (the delta-rule scan without the delta);
+* a fourth kind, "hyper", keeps several copies of the stream that learned weights mix at every sublayer (hyper-connections) with a
+  layer norm (weight and bias) in front of each sublayer; its mixers are rotated attention with optional terms (biases, unit norm of
+  q / k, capped scores, a sink, kept first positions, a bias by distance bucket, values that are the keys, two differential score
+  maps, pages borrowed from an earlier layer) and a matrix memory with exponential gates (mLSTM); its router may limit the choice to
+  the best groups of experts;
 * the residual stream, its depth-weighted average, norms, scores, softmax, decays and recurrent state are float32 in both
   serving modes; ``dtype="bf16"`` keeps GEMM operands and KV pages in bf16 (fp32 accumulation, fp32 GEMM results),
   ``dtype="fp32"`` keeps everything in float32 with TF32 off;
@@ -29,6 +34,7 @@ step in a per-sequence slot) and it gives chunked prefill and continuous batchin
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -63,7 +69,7 @@ class StepPlan:
 
 class _Mixer:
     __slots__ = ("spec", "cols", "out_col", "out_size", "vec", "k_cache", "v_cache", "conv_state", "state", "w_lr2", "lr_cols", "rank",
-                 "w_uk", "w_uv", "rot_mult")
+                 "w_uk", "w_uv", "rot_mult", "aux_state", "lam", "owns_kv")
 
 
 class _Layer:
@@ -71,7 +77,8 @@ class _Layer:
     feed-forward side by side), or one sublayer of a sandwich stream (the mixer, or the feed-forward)."""
     __slots__ = ("spec", "gain", "dw", "w_in", "w_out", "mixers", "ff_col", "ff_out_col", "n_in", "k_out", "out_pad",
                  "w_pre", "w_post", "gate_col", "gate_bias", "router_col", "router_bias", "w_gate_up", "w_down",
-                 "shared_col", "shared_out_col", "sg_col", "side_col", "side_out_col", "side_col0")
+                 "shared_col", "shared_out_col", "sg_col", "side_col", "side_out_col", "side_col0", "hc_in", "hc_out", "hc_mix", "w_pre_b",
+                 "out_bias")
 
 
 def _pad8(n: int) -> int:
@@ -164,6 +171,17 @@ class HybridSampler:
                     L = self._build_stage(spec, [], False, side=True)
                     L.w_post = self._f(p + "side.norm")
                     self.layers.append(L)
+            elif st.kind == "hyper":                      # two stages per layer, each behind its own layer norm and stream weights
+                for k, (mixers, ff) in enumerate(((spec.mixers, False), ([], True))):
+                    if ff and not spec.ff:
+                        continue
+                    n = str(k + 1)
+                    L = self._build_stage(spec, mixers, ff)
+                    L.w_pre = self._f(p + "norm" + n)
+                    L.w_pre_b = self._f(p + "norm" + n + ".b") if lm.has_tensor(p + "norm" + n + ".b") else None
+                    if st.hyper_weights:
+                        L.hc_in, L.hc_out, L.hc_mix = (self._f(f"{p}hc{n}.{x}") for x in ("in", "out", "mix"))
+                    self.layers.append(L)
             else:
                 raise ValueError(f"unknown stream kind {st.kind!r}")
         self.embed_gain = self._f("embed.norm") if st.kind == "post_norm" else None
@@ -173,9 +191,10 @@ class HybridSampler:
         self.pos_table = self._t("pos").to(device=dev, dtype=wd).contiguous() if st.positions else None
         self.pair_table = self._t("bigram").to(device=dev, dtype=wd).contiguous() if st.pair_buckets else None
         self.final_gain = self._f("final.norm").reshape(1) if st.kind == "depth_weighted" else self._f("final.norm")
+        self.final_bias = self._f("final.norm.b") if st.kind == "hyper" and lm.has_tensor("final.norm.b") else None
         V = self.cfg.vocab
         self.head = torch.zeros(_pad8(V), W, dtype=wd, device=dev)
-        self.head[:V] = self._t("head").to(device=dev, dtype=wd)
+        self.head[:V] = self._t("embed" if st.tied_head else "head").to(device=dev, dtype=wd)
         self._weights_version = self.weights_fingerprint()
 
     def _build_stage(self, spec, mixer_specs, with_ff: bool, gate: Optional[str] = None, side: bool = False) -> _Layer:
@@ -188,6 +207,7 @@ class HybridSampler:
         L.gain = L.dw = L.w_pre = L.w_post = L.gate_col = L.gate_bias = L.router_col = L.router_bias = None
         L.w_gate_up = L.w_down = None
         L.shared_col = L.shared_out_col = L.sg_col = L.side_col = L.side_out_col = None
+        L.hc_in = L.hc_out = L.hc_mix = L.w_pre_b = L.out_bias = None
         L.side_col0 = 0
         rows_in: List[torch.Tensor] = []
         cols_out: List[torch.Tensor] = []
@@ -196,7 +216,7 @@ class HybridSampler:
 
         def add_in(name):
             nonlocal n_in
-            t = self._t(name)
+            t = self._t(name) if isinstance(name, str) else name
             rows_in.append(t)
             c = (n_in, t.shape[0])
             n_in += t.shape[0]
@@ -220,7 +240,8 @@ class HybridSampler:
         for ms in mixer_specs:
             M = _Mixer()
             M.spec, M.cols, M.vec = ms, {}, {}
-            M.k_cache = M.v_cache = M.conv_state = M.state = M.w_lr2 = M.w_uk = M.w_uv = None
+            M.k_cache = M.v_cache = M.conv_state = M.state = M.w_lr2 = M.w_uk = M.w_uv = M.aux_state = None
+            M.lam, M.owns_kv = 0.0, True
             q = ms.prefix
             if ms.kind == "window_attention":
                 for n in ("q", "k", "v"):
@@ -285,6 +306,51 @@ class HybridSampler:
                 w2[:a2.shape[0], :M.rank] = a2.to(wd)
                 M.w_lr2 = w2
                 M.vec["a2.b"], M.vec["norm"] = self._f(q + "a2.b"), self._f(q + "norm")
+            elif ms.kind == "rot_attention":
+                wq = self._t(q + "q")
+                if ms.maps == 2:
+                    # the two score maps become heads of their own: query rows [H, map, dim] are reordered to (key/value head, map,
+                    # query head of the group), so that the kernels' grouping (consecutive query heads share a key head) pairs map m of
+                    # a head with key head 2 g + m; the read side undoes the order
+                    R = ms.heads // ms.kv_heads
+                    wq = wq.reshape(ms.kv_heads, R, 2, ms.dim, W).permute(0, 2, 1, 3, 4).reshape(2 * ms.heads * ms.dim, W)
+                M.cols["q"] = add_in(wq)
+                M.owns_kv = ms.kv_from < 0
+                if M.owns_kv:
+                    M.cols["k"] = add_in(q + "k")
+                    if not ms.values_from_keys:
+                        M.cols["v"] = add_in(q + "v")
+                if ms.out_gate:
+                    M.cols["g"] = add_in(q + "g")
+                if ms.qk_bias:
+                    qb = self._f(q + "q.b")
+                    if ms.maps == 2:
+                        qb = qb.reshape(ms.kv_heads, ms.heads // ms.kv_heads, 2, ms.dim).permute(0, 2, 1, 3).reshape(-1).contiguous()
+                    M.vec["q.b"] = qb
+                    if M.owns_kv:
+                        M.vec["k.b"] = self._f(q + "k.b")
+                if ms.head_sink:
+                    M.vec["sink"] = self._f(q + "sink")
+                if ms.bias_max:                            # one row per distance 0 .. bias_max (the last one holds from there on)
+                    M.vec["rel"] = hy.distance_bias_table(self._f(q + "rel"), ms.bias_max)
+                if ms.rot_dims:
+                    freq, M.rot_mult = hy.rotary_frequencies(ms.rot_dims, ms.rot_base, ms.rot_scaling)
+                    M.vec["freq"] = torch.tensor(freq, dtype=torch.float64, device=dev)
+                else:
+                    M.rot_mult = 1.0
+                if ms.maps == 2:
+                    l1 = (self._t(q + "lq1").double() * self._t(q + "lk1").double()).sum().item()
+                    l2 = (self._t(q + "lq2").double() * self._t(q + "lk2").double()).sum().item()
+                    M.lam = math.exp(l1) - math.exp(l2) + ms.diff
+                if ms.out_bias:
+                    b = self._f(q + "o.b") * ms.out_scale
+                    L.out_bias = b if L.out_bias is None else L.out_bias + b
+            elif ms.kind == "mlstm":
+                for n in ("q", "k", "v", "g", "i", "f"):
+                    M.cols[n] = add_in(q + n)
+                pad_in()
+                for n in ("i.b", "f.b", "norm"):
+                    M.vec[n] = self._f(q + n)
             else:
                 raise ValueError(f"unknown mixer kind {ms.kind!r}")
             M.out_col, M.out_size = add_out(q + "o")
@@ -367,12 +433,12 @@ class HybridSampler:
     def sync_weights(self, force: bool = False):
         """Re-fuse the arena when the model's weights changed (the optimizer bumps ``_nrl_version``)."""
         if force or self._weights_version != self.weights_fingerprint():
-            pools = [(M.k_cache, M.v_cache, M.conv_state, M.state) for L in self.layers for M in L.mixers]
+            pools = [(M.k_cache, M.v_cache, M.conv_state, M.state, M.aux_state) for L in self.layers for M in L.mixers]
             self._graphs.clear()                          # captured graphs hold the old arena's addresses
             self._graph_seen.clear()
             self._build_arena()
             for M, pl in zip([M for L in self.layers for M in L.mixers], pools):
-                M.k_cache, M.v_cache, M.conv_state, M.state = pl
+                M.k_cache, M.v_cache, M.conv_state, M.state, M.aux_state = pl
 
     def release(self):
         self._graphs.clear()
@@ -403,6 +469,13 @@ class HybridSampler:
                     M.k_cache = torch.zeros(n, 1, self.PAGE, ms.kv_rank + ms.rot_dim, dtype=wd, device=dev)
                 elif ms.kind == "gla":
                     M.state = torch.zeros(num_slots, ms.heads, ms.dim, ms.vdim, **f32)
+                elif ms.kind == "rot_attention":
+                    if M.owns_kv:                          # every score map has key heads of its own; the values are shared by the maps
+                        M.k_cache = torch.zeros(n, ms.maps * ms.kv_heads, self.PAGE, ms.dim, dtype=wd, device=dev)
+                        M.v_cache = torch.zeros(n, ms.kv_heads, self.PAGE, ms.vdim, dtype=wd, device=dev)
+                elif ms.kind == "mlstm":                   # S with the normaliser n as column vdim (rows padded to 32 bytes); the running maximum
+                    M.state = torch.zeros(num_slots, ms.heads, ms.dim, _pad8(ms.vdim + 1), **f32)
+                    M.aux_state = torch.zeros(num_slots, ms.heads, **f32)
                 elif ms.kind == "ssd":
                     ch = ms.heads * ms.vdim + 2 * ms.kv_heads * ms.dim
                     M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
@@ -411,6 +484,11 @@ class HybridSampler:
                     ch = 2 * ms.kv_heads * ms.dim + ms.heads * ms.vdim
                     M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
                     M.state = torch.zeros(num_slots, ms.heads, ms.dim, ms.vdim, **f32)
+        for L in self.layers:                             # layers that read an earlier layer's pages
+            for M in L.mixers:
+                if M.spec.kind == "rot_attention" and not M.owns_kv:
+                    src = next(m for l in self.layers if l.spec.index == M.spec.kv_from for m in l.mixers if m.spec.kind == "rot_attention")
+                    M.k_cache, M.v_cache = src.k_cache, src.v_cache
         # the last token of every sequence (hashed pair embedding): part of a sequence's state like the convolution taps
         self.prev_token = torch.zeros(num_slots, dtype=torch.int32, device=dev) if self.stream.pair_buckets else None
         self.num_blocks, self.num_slots = n, num_slots
@@ -490,6 +568,8 @@ class HybridSampler:
             return self._forward_sandwich(plan, rows)
         if self.stream.kind == "post_norm":
             return self._forward_post_norm(plan, rows)
+        if self.stream.kind == "hyper":
+            return self._forward_hyper(plan, rows)
         return self._forward_depth_weighted(plan, rows)
 
     def _run_mixers(self, L, U, A, plan, eps, ctx=None):
@@ -500,6 +580,10 @@ class HybridSampler:
                 self._latent_attention(M, U, plan, eps, out)
             elif kind == "gla":
                 self._gla(M, U, plan, eps, out)
+            elif kind == "rot_attention":
+                self._rot_attention(M, U, plan, eps, out)
+            elif kind == "mlstm":
+                self._mlstm(M, U, plan, eps, out)
             elif kind == "conv_attention":
                 self._conv_attention(M, U, plan, out, ctx, L.spec.index)
             elif kind == "gated_delta":
@@ -544,6 +628,86 @@ class HybridSampler:
             return torch.empty(0, cfg.vocab, **f32)
         hw = h if rows == list(range(T)) else h[torch.tensor(rows, device=dev)]
         return self._mm(hw.contiguous(), self.head)[:, :cfg.vocab]
+
+    def _forward_hyper(self, plan: StepPlan, rows: List[int], keep: Optional[list] = None) -> torch.Tensor:
+        """Several copies of the stream mixed by learned weights.  One fused kernel per sublayer boundary closes the sublayer (all
+        streams from the old ones plus its result, output bias and identity experts' share included) and forms the next sublayer's
+        layer-normed input (the last one: the final norm of the streams' sum).  ``keep``: a list that receives the sum of the streams
+        after every layer."""
+        cfg, dev, wd, st = self.cfg, self.device, self.wdtype, self.stream
+        T, W, eps = plan.T, cfg.width, cfg.norm_eps
+        f32 = dict(dtype=torch.float32, device=dev)
+        xs = torch.empty(T, st.streams, W, **f32)
+        hy.embed_streams(self.embed, plan.tokens, st.embed_scale, xs)
+        h = torch.empty(T, W, dtype=wd, device=dev)
+        first = self.layers[0]
+        hy.hyper_boundary(xs, None, None, None, None, None, first.hc_in, first.w_pre, first.w_pre_b, eps, h)
+        for i, L in enumerate(self.layers):
+            U = self._mm(h, L.w_in)                                                   # [T, n_in] float
+            A = (torch.zeros if L.out_pad else torch.empty)(T, L.k_out, dtype=wd, device=dev)
+            self._run_mixers(L, U, A, plan, eps)
+            self_w = None
+            if L.ff_col is not None:
+                self_w = self._feed_forward(L, U, A)
+            o = self._mm(A, L.w_out) if L.k_out else None                             # [T, W] float
+            if L.w_gate_up is not None:
+                o, self_w = self._experts_grouped(L, U, h, o, want_self=True)
+            last = i + 1 == len(self.layers)
+            nxt = None if last else self.layers[i + 1]
+            hy.hyper_boundary(xs, o, L.out_bias, self_w, L.hc_mix, L.hc_out, None if last else nxt.hc_in,
+                              self.final_gain if last else nxt.w_pre, self.final_bias if last else nxt.w_pre_b, eps, h)
+            if keep is not None and (last or nxt.spec.index != L.spec.index):
+                keep.append(xs.sum(1))
+        if not rows:
+            return torch.empty(0, cfg.vocab, **f32)
+        hw = h if rows == list(range(T)) else h[torch.tensor(rows, device=dev)]
+        return self._mm(hw.contiguous(), self.head)[:, :cfg.vocab]
+
+    def _rot_attention(self, M, U, plan, eps, out):
+        """Attention with rotated (or plain) grouped heads and the optional terms of its spec.  One launch finishes the queries in
+        place (bias, rotation, unit norm) and writes keys and values to their pages; the paged kernel applies cap, distance bias,
+        window with kept first positions and sink; two differential maps run as heads of their own over shared values and are
+        combined, normed and gated by one more launch."""
+        ms = M.spec
+        T, dev = plan.T, U.device
+        cq, nq = M.cols["q"]
+        q = U[:, cq:cq + nq]
+        k = v = None
+        if M.owns_kv:
+            ck, nk = M.cols["k"]
+            k = U[:, ck:ck + nk]
+            if not ms.values_from_keys:
+                cv, nv = M.cols["v"]
+                v = U[:, cv:cv + nv]
+        hy.rot_kv_write(q, M.vec.get("q.b"), k, M.vec.get("k.b"), v, M.vec.get("freq"), ms.rot_dims, M.rot_mult,
+                        ms.rot_layout == "interleaved", ms.unit_qk_norm, None, None, eps, plan, M.k_cache, M.v_cache)
+        window = ms.window if ms.window > 0 else 1 << 30
+        gate = None
+        if ms.out_gate:
+            cg, ng = M.cols["g"]
+            gate = U[:, cg:cg + ng]
+        if ms.maps == 2:
+            a = torch.empty(T, 2 * ms.heads * ms.vdim, dtype=self.wdtype, device=dev)
+            hy.window_attention(q, M.k_cache, M.v_cache, plan, window, ms.scale, 1.0, a, head_sink=M.vec.get("sink"), softcap=ms.softcap,
+                                keep_first=ms.keep_first, dist_bias=M.vec.get("rel"), v_div=2)
+            hy.diff_combine(a, M.lam, 1.0 - ms.diff, eps, gate, ms.out_scale, out, ms.heads, ms.kv_heads)
+            return
+        if gate is not None:
+            raise NotImplementedError("an element-wise output gate goes with two score maps")
+        hy.window_attention(q, M.k_cache, M.v_cache, plan, window, ms.scale, ms.out_scale, out, head_sink=M.vec.get("sink"),
+                            softcap=ms.softcap, keep_first=ms.keep_first, dist_bias=M.vec.get("rel"))
+
+    def _mlstm(self, M, U, plan, eps, out):
+        """Matrix memory with exponential gates: the scan carries S, the normaliser and the running maximum per slot and reads the
+        projections where the fused GEMM left them; a second launch divides, norms per head, weights and gates."""
+        ms = M.spec
+        T, dev = plan.T, U.device
+        o = torch.empty(T, ms.heads * (ms.vdim + 1), dtype=torch.float32, device=dev)
+        m = torch.empty(T, ms.heads, dtype=torch.float32, device=dev)
+        hy.mlstm_scan(U, M.cols["q"][0], M.cols["k"][0], M.cols["v"][0], M.cols["i"][0], M.cols["f"][0], M.vec["i.b"], M.vec["f.b"],
+                      ms.gate_cap, ms.dim ** -0.5, M.state, M.aux_state, o, m, plan)
+        cg, ng = M.cols["g"]
+        hy.mlstm_out(o, m, U[:, cg:cg + ng], M.vec["norm"], eps, ms.out_scale, out, ms.heads)
 
     def _latent_attention(self, M, U, plan, eps, out):
         """Latent attention in its absorbed form.  The cache holds one row [latent | rotated shared key part] per token; a head's
@@ -660,7 +824,8 @@ class HybridSampler:
         if spec.route == "softmax_all":
             if spec.identity_experts:
                 self_w = torch.empty(T, dtype=torch.float32, device=dev)
-            hy.moe_route_all(U[:, rc:rc + E], L.router_bias, spec.experts, spec.top, spec.route_scale, ids=ids, wts=wts, self_w=self_w)
+            hy.moe_route_all(U[:, rc:rc + E], L.router_bias, spec.experts, spec.top, spec.route_scale, ids=ids, wts=wts, self_w=self_w,
+                             groups=spec.route_groups, keep=spec.route_keep)
         else:
             hy.moe_route(U[:, rc:rc + E], L.router_bias, spec.top, ids=ids, wts=wts)
         y = torch.empty(T, self.cfg.width, dtype=torch.float32, device=dev)
@@ -679,7 +844,7 @@ class HybridSampler:
             rc, E = L.router_col
             self_w = torch.empty(U.shape[0], dtype=torch.float32, device=U.device) if spec.identity_experts else None
             hy.moe_route_all(U[:, rc:rc + E], L.router_bias, spec.experts, spec.top, spec.route_scale, gu=U[:, c:c + n], ff=spec.ff,
-                             act=A[:, oc:oc + on], self_w=self_w)
+                             act=A[:, oc:oc + on], self_w=self_w, groups=spec.route_groups, keep=spec.route_keep)
             return self_w
         if spec.ff_kind == "moe":
             rc, E = L.router_col
