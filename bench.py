@@ -59,10 +59,10 @@ def parse():
                     help="instead of the GRPO update: prefill / decode throughput of the hybrid step engine (Nezavik) beside the "
                          "Qwen2 engine at equal size, and every new kernel against its roofline (bench/serve_bench.py; one GPU)")
     ap.add_argument("--serve-quick", action="store_true", help="with --serve-bench: one small end-to-end size")
-    ap.add_argument("--serve-model", default="nezavik", choices=["nezavik", "vilosun", "damilix"],
+    ap.add_argument("--serve-model", default="nezavik", choices=["nezavik", "vilosun", "damilix", "lukarax"],
                     help="with --serve-bench: nezavik = Nezavik beside Qwen2; vilosun = Vilosun beside Nezavik (same step engine) at "
                          "equal width and depth, and the kernels Vilosun adds beside Nezavik's like kernels; damilix = Damilix beside "
-                         "Vilosun in the same way")
+                         "Vilosun in the same way; lukarax = Lukarax beside Damilix")
     return ap.parse_args()
 
 

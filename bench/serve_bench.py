@@ -1,7 +1,7 @@
 """Serving throughput of the hybrid step engine (Nezavik) beside the paged-KV transformer engine (Qwen2) at equal size,
 plus each new kernel against its roofline and against the like kernel of the transformer path; with ``--serve-model vilosun``
 the Vilosun family beside Nezavik (same engine) at equal size, and the kernels it adds beside Nezavik's like kernels; with
-``--serve-model damilix`` the Damilix family beside Vilosun in the same way.
+``--serve-model damilix`` the Damilix family beside Vilosun in the same way, ``--serve-model lukarax`` the Lukarax family beside Damilix.
 
 Run through ``python bench.py --serve-bench`` (one GPU).  Random weights, synthetic token ids.  End-to-end numbers go
 through the engines' public ``generate`` (two runs that differ by `new` generated tokens: the difference is `new` decode steps,
@@ -399,6 +399,187 @@ def kernels_damilix(width=2048, batch=16, prompt_len=2048, decode_batch=256, ctx
     return out
 
 
+def lukarax_config(width: int, n_layers: int, vocab: int, experts: int = 16, top: int = 2, streams: int = 4):
+    """Heads of 128 columns, four query heads per key/value head; layer pattern parallel (windowed attention with kept first keys and
+    a distance bias beside a matrix memory with 128 x 128 states) / attention_2 / attention / attention reading the pages of the
+    layer before; experts as in ``damilix_config`` (two identity experts, groups of neighbours, no shared expert)."""
+    from nanorlhf_b200.models.lukarax import LukaraxConfig
+    H = width // 128
+    G = max(1, H // 4)
+    ff = max(128, (8 * width // (3 * top) + 127) // 128 * 128)
+    n_out = experts + 2
+    groups = next(g for g in (6, 4, 3, 2, 1) if n_out % g == 0)
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "identity": 2, "top": top, "scale": 1.5,
+                                                             "groups": {"count": groups, "keep": max(1, groups // 2)}}}
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": {"heads": H // 2, "kv_heads": max(1, G // 2), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "bias_max": 2048,
+                              "mask": {"size": 1024, "keep_first": 64}},
+                     "right": {"heads": H // 2, "dim": 128, "vdim": 128, "gate_cap": 15.0}, "left_scale": 0.7, "right_scale": 1.0}}
+    a2 = {"type": "attention_2", "mlp": mlp,
+          "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 1.0, "softcap": 50.0, "mask": {"size": 1024},
+                    "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    da = {"type": "attention", "mlp": mlp,
+          "mixer": {"heads": H // 2, "kv_heads": max(1, G // 2), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "diff": 0.2,
+                    "rot": {"base": 1e6, "dims": 128}}}
+    layers = []
+    for i in range(n_layers):
+        layer = json.loads(json.dumps([par, a2, da, da][i % 4]))
+        if i % 4 == 3:
+            layer["mixer"]["kv_from"] = i - 1
+        layers.append(layer)
+    return LukaraxConfig.from_dict({"architecture": "Lukarax", "layers": layers, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+                                    "streams": streams, "vocab": vocab, "width": width})
+
+
+def end_to_end_lukarax(width, n_layers, batch, prompt_len, new=128, vocab=32768):
+    """Lukarax beside Damilix (the closest family: same engine, attention + recurrent layers, routed experts with identity experts)
+    at equal width, depth and expert sizes."""
+    from nanorlhf_b200.models.damilix import DamilixForCausalLM
+    from nanorlhf_b200.models.lukarax import LukaraxForCausalLM
+    from nanorlhf_b200.sampler.hybrid_sampler import HybridSampler
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, vocab - 2, (batch, prompt_len), generator=g).tolist()
+    res = {"width": width, "layers": n_layers, "batch": batch, "prompt_len": prompt_len, "new_tokens": new}
+    for name, make in (("lukarax", lambda: LukaraxForCausalLM.from_config(lukarax_config(width, n_layers, vocab), torch.bfloat16, dev, seed=0)),
+                       ("damilix", lambda: DamilixForCausalLM.from_config(damilix_config(width, n_layers, vocab), torch.bfloat16, dev, seed=0, gla_rank=64))):
+        model = make()
+        eng = HybridSampler(model, dtype="bf16", max_num_seqs=batch, prefill_token_budget=16384)
+        pre, step = _gen_times(lambda p, mt: eng.generate(p, 1, 1.0, 1.0, mt, None, vocab - 1, 1), prompts, new)
+        res[name] = {"params_m": round(sum(p.numel() for p in model.parameters()) / 1e6, 1),
+                     "prefill_tok_s": round(batch * prompt_len / pre), "decode_tok_s": round(batch / step),
+                     "decode_ms_per_step": round(step * 1e3, 3)}
+        eng.release()
+        del eng, model
+        torch.cuda.empty_cache()
+    return res
+
+
+def kernels_lukarax(width=2048, batch=16, prompt_len=2048, decode_batch=256, ctx=2048, experts=16, top=2, streams=4, window=1024):
+    """The kernels Lukarax adds to the step engine, each beside the like kernel of the Damilix / Vilosun / Nezavik paths."""
+    from nanorlhf_b200 import _C
+    from nanorlhf_b200.ops import hybrid as hy
+    from nanorlhf_b200.sampler.hybrid_sampler import StepPlan
+    hbm, flops_peak, which = _peaks()
+    dev = torch.device("cuda:0")
+    out = {"roofline": which, "width": width}
+    H, Hkv, D = width // 128, max(1, width // 512), 128
+
+    def plan_for(B, n_new, n_old):
+        s = _C.StepScheduler((n_old + n_new + 15) // 16 * B + 8, 16, B)
+        sids = [s.open() for _ in range(B)]
+        if n_old:
+            s.plan(sids, [n_old] * B)
+        data, E, T, MB = s.plan(sids, [n_new] * B)
+        return StepPlan(torch.from_numpy(data).to(dev), E, T, MB), s
+
+    def report(name, sec, bytes_, flops=0.0):
+        floor = max(bytes_ / hbm, flops / flops_peak)
+        out[name] = {"us": round(sec * 1e6, 1), "gb_s": round(bytes_ / sec / 1e9, 1), "tflop_s": round(flops / sec / 1e12, 2),
+                     "roofline_frac": round(floor / sec, 3)}
+
+    for phase, B, n_new, n_old in (("prefill", batch, prompt_len, 0), ("decode", decode_batch, 1, ctx - 1)):
+        plan, sched = plan_for(B, n_new, n_old)
+        T = plan.T
+        f32 = dict(dtype=torch.float32, device=dev)
+        plan.tokens.copy_(torch.randint(0, 32000, (T,), dtype=torch.int32, device=dev))
+        # -- embedding into every stream vs the normed embedding
+        emb = torch.randn(32768, width, device=dev).bfloat16()
+        xs, h = torch.empty(T, streams, width, **f32), torch.empty(T, width, dtype=torch.bfloat16, device=dev)
+        x0, wa, wb = torch.empty(T, width, **f32), torch.ones(width, **f32), torch.zeros(width, **f32)
+        sec = _time(lambda: hy.embed_streams(emb, plan.tokens, 2.0, xs))
+        report(f"{phase}.embed_streams(S={streams})", sec, T * width * (2.0 + 4.0 * streams))
+        sec = _time(lambda: hy.embed_norm(emb, plan.tokens, wa, 1e-6, x0, h))
+        report(f"{phase}.damilix.embed_norm", sec, T * width * 8.0)
+        # -- sublayer boundary over S streams (read and write all of them) vs one stream
+        o, sw, ob = torch.randn(T, width, **f32), torch.rand(T, **f32), torch.randn(width, **f32)
+        mix, ow, iw = torch.eye(streams, **f32) + 0.1, torch.ones(streams, **f32), torch.full((streams,), 0.3, **f32)
+        xs.normal_()
+        sec = _time(lambda: hy.hyper_boundary(xs, o, ob, sw, mix, ow, iw, wa, wb, 1e-6, h))
+        report(f"{phase}.hyper_boundary(S={streams})", sec, T * width * (8.0 * streams + 4.0 + 2.0 * 2))
+        x = torch.randn(T, width, **f32)
+        sec = _time(lambda: hy.post_norm_residual(x, o, sw, wa, None, 1e-6, h))
+        report(f"{phase}.damilix.post_norm_residual", sec, T * width * (4.0 * 3 + 2))
+        del xs, x, o
+        # -- routing with and without groups
+        zr, corr = torch.randn(T, experts + 2, **f32), torch.randn(experts + 2, **f32) * 0.01
+        ids, wts, selfw = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, **f32), torch.empty(T, **f32)
+        groups = next(g for g in (6, 4, 3, 2, 1) if (experts + 2) % g == 0)
+        rb = T * ((experts + 2) * 4.0 + top * 8.0 + 4.0)
+        sec = _time(lambda: hy.moe_route_all(zr, corr, experts, top, 1.5, ids=ids, wts=wts, self_w=selfw, groups=groups, keep=max(1, groups // 2)))
+        report(f"{phase}.moe_route_all(groups={groups})", sec, rb)
+        sec = _time(lambda: hy.moe_route_all(zr, corr, experts, top, 1.5, ids=ids, wts=wts, self_w=selfw))
+        report(f"{phase}.damilix.moe_route_all", sec, rb)
+        # -- write side: bias + rotation + unit norm + pages vs q / k norm + pages
+        n_pages = sched.num_free_blocks() + plan.max_blocks * B + 8
+        nq, nk = H * D, Hkv * D
+        q, k_, v_ = torch.randn(T, nq, **f32), torch.randn(T, nk, **f32), torch.randn(T, nk, **f32)
+        qb, kb = torch.randn(nq, **f32), torch.randn(nk, **f32)
+        kc = torch.randn(n_pages, Hkv, 16, D, device=dev).bfloat16()
+        vc = torch.randn_like(kc)
+        fr, mult = hy.rotary_frequencies(64, 1e6, {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+        freq = torch.tensor(fr, dtype=torch.float64, device=dev)
+        sec = _time(lambda: hy.rot_kv_write(q, qb, k_, kb, None, freq, 64, mult, False, True, None, None, 1e-6, plan, kc, vc))
+        report(f"{phase}.rot_kv_write(values = keys)", sec, T * (nq * 8.0 + nk * (4.0 + 4.0)))
+        sec = _time(lambda: hy.rot_kv_write(q, None, k_, None, v_, freq, 64, mult, True, False, None, None, 1e-6, plan, kc, vc))
+        report(f"{phase}.rot_kv_write(q, k, v)", sec, T * (nq * 8.0 + nk * (8.0 + 4.0)))
+        sec = _time(lambda: hy.qknorm_kv_write(q, k_, v_, torch.ones(D, **f32), torch.ones(D, **f32), 1e-6, kc, vc, plan))
+        report(f"{phase}.nezavik.qknorm_kv_write", sec, T * (nq * 8.0 + nk * (8.0 + 4.0)))
+        # -- attention forms
+        q.normal_()
+        ao = torch.empty(T, nq, dtype=torch.bfloat16, device=dev)
+        it, wm = (3, 1) if phase == "prefill" else (20, 5)
+        sink = torch.randn(H, **f32)
+        keys_w = (sum(min(p + 1, window) for p in range(n_new)) if phase == "prefill" else min(ctx, window)) * B
+        byt_w = (T * H * D * 6.0 + T * 2 * Hkv * D * 2.0) if phase == "prefill" else (keys_w * 2 * Hkv * D * 2.0 + T * H * D * 6.0)
+        sec = _time(lambda: hy.window_attention(q, kc, vc, plan, window, 1.0, 1.0, ao, head_sink=sink, softcap=50.0), iters=it, warm=wm)
+        report(f"{phase}.attention(window {window}, cap, sink)", sec, byt_w, flops=4.0 * keys_w * H * D)
+        table = torch.randn(2049, H, **f32) * 0.1
+        keys_k = keys_w + (sum(min(64, max(0, p + 1 - window)) for p in range(n_new)) if phase == "prefill" else min(64, max(0, ctx - window))) * B
+        sec = _time(lambda: hy.window_attention(q, kc, vc, plan, window, D ** -0.5, 1.0, ao, keep_first=64, dist_bias=table), iters=it, warm=wm)
+        report(f"{phase}.attention(window {window}, kept 64, distance bias)", sec, byt_w * keys_k / keys_w if phase == "decode" else byt_w,
+               flops=4.0 * keys_k * H * D)
+        sec = _time(lambda: hy.window_attention(q, kc, vc, plan, window, D ** -0.5, 1.0, ao), iters=it, warm=wm)
+        report(f"{phase}.nezavik.window_attention(window {window})", sec, byt_w, flops=4.0 * keys_w * H * D)
+        # two score maps over shared values: twice the query and key heads, one set of values
+        kc2 = torch.randn(n_pages, 2 * Hkv, 16, D, device=dev).bfloat16()
+        a2 = torch.empty(T, 2 * H * D, dtype=torch.bfloat16, device=dev)
+        q2 = torch.randn(T, 2 * nq, **f32)
+        keys_c = (sum(p + 1 for p in range(n_new)) if phase == "prefill" else ctx) * B
+        byt_c = (T * 2 * H * D * 6.0 + T * 3 * Hkv * D * 2.0) if phase == "prefill" else (keys_c * 3 * Hkv * D * 2.0 + T * 2 * H * D * 6.0)
+        sec = _time(lambda: hy.window_attention(q2, kc2, vc, plan, 1 << 30, D ** -0.5, 1.0, a2, v_div=2), iters=it, warm=wm)
+        report(f"{phase}.attention(causal, two maps, shared values)", sec, byt_c, flops=4.0 * keys_c * 2 * H * D)
+        kc1 = torch.randn(n_pages, 2 * Hkv, 16, D, device=dev).bfloat16()
+        sec = _time(lambda: hy.window_attention(q2, kc2, kc1, plan, 1 << 30, D ** -0.5, 1.0, a2), iters=it, warm=wm)
+        report(f"{phase}.nezavik.window_attention(causal, twice the heads)", sec, byt_c + (T if phase == "prefill" else keys_c) * Hkv * D * 2.0,
+               flops=4.0 * keys_c * 2 * H * D)
+        gate = torch.randn(T, nq, **f32)
+        sec = _time(lambda: hy.diff_combine(a2, 0.4, 0.7, 1e-6, gate, 1.0, ao, H, Hkv))
+        report(f"{phase}.diff_combine", sec, T * nq * (4.0 + 4.0 + 2.0))
+        del kc, vc, kc2, kc1, a2, q2
+        # -- matrix memory vs gated linear attention (same state size) and their read-out norms
+        nkk = H * D
+        U = torch.randn(T, 3 * nkk + 2 * H, **f32) * 0.1
+        state, mst = torch.zeros(B, H, D, D + 8, **f32), torch.zeros(B, H, **f32)
+        om, mo = torch.empty(T, H * (D + 1), **f32), torch.empty(T, H, **f32)
+        ib = torch.zeros(H, **f32)
+        sec = _time(lambda: hy.mlstm_scan(U, 0, nkk, 2 * nkk, 3 * nkk, 3 * nkk + H, ib, ib, 15.0, D ** -0.5, state, mst, om, mo, plan), iters=3, warm=1)
+        sbytes = B * H * D * D * 8.0 + T * nkk * 16.0
+        report(f"{phase}.mlstm_scan", sec, sbytes)
+        out[f"{phase}.mlstm_scan"]["fp32_fma_frac"] = round(4.0 * T * H * D * (D + 1) / sec / 72e12, 3)
+        nw = torch.ones(nkk, **f32)
+        sec = _time(lambda: hy.mlstm_out(om, mo, gate, nw, 1e-6, 1.0, ao, H))
+        report(f"{phase}.mlstm_out", sec, T * nkk * (4.0 + 4.0 + 2.0))
+        qkv, decay, og = torch.randn(T, 3 * nkk, **f32) * 0.1, torch.rand(T, nkk, **f32) * 0.1 + 0.9, torch.empty(T, nkk, **f32)
+        st2 = torch.zeros(B, H, D, D, **f32)
+        sec = _time(lambda: hy.delta_scan(qkv, nkk, 2 * nkk, None, decay, st2, og, plan, H, True), iters=3, warm=1)
+        report(f"{phase}.damilix.gla_scan", sec, B * H * D * D * 8.0 + T * nkk * 20.0)
+        out[f"{phase}.damilix.gla_scan"]["fp32_fma_frac"] = round(4.0 * T * H * D * D / sec / 72e12, 3)
+        sec = _time(lambda: hy.gated_part_rmsnorm(og, gate, torch.ones(D, **f32), D, "silu", False, 1e-6, 1.0, ao))
+        report(f"{phase}.damilix.gated_part_rmsnorm", sec, T * nkk * (4.0 + 4.0 + 2.0))
+    return out
+
+
 def end_to_end(width, n_layers, batch, prompt_len, new=128, vocab=32768):
     from nanorlhf_b200.models.nezavik import NezavikForCausalLM
     from nanorlhf_b200.models.qwen2 import Qwen2Config, Qwen2ForCausalLM
@@ -550,6 +731,18 @@ def main(quick: bool = False, small: bool = False, model: str = "nezavik"):
     from nanorlhf_b200.ops import native
     global SMALL
     native.load()
+    if model == "lukarax":
+        SMALL = small
+        if small:
+            print(json.dumps({"bench": "serve-lukarax-small",
+                              "kernels": kernels_lukarax(width=1024, batch=8, prompt_len=1024, decode_batch=64, ctx=1024)}))
+            return None
+        res = {"bench": "serve-lukarax", "kernels": kernels_lukarax(), "end_to_end": []}
+        for width, layers, batch, plen in ((1024, 8, 32, 1024), (2048, 8, 16, 2048)) if not quick else ((1024, 4, 8, 512),):
+            res["end_to_end"].append(end_to_end_lukarax(width, layers, batch, plen))
+        res["gpu_launches"] = native.launches()
+        print(json.dumps(res))
+        return res
     if model == "damilix":
         SMALL = small
         if small:
@@ -588,4 +781,4 @@ def main(quick: bool = False, small: bool = False, model: str = "nezavik"):
 
 if __name__ == "__main__":
     main(quick="--quick" in sys.argv, small="--small" in sys.argv,
-         model="damilix" if "--damilix" in sys.argv else "vilosun" if "--vilosun" in sys.argv else "nezavik")
+         model="lukarax" if "--lukarax" in sys.argv else "damilix" if "--damilix" in sys.argv else "vilosun" if "--vilosun" in sys.argv else "nezavik")
