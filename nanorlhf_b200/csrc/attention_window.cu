@@ -254,7 +254,9 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
   for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
     float a = 0.f;
     for (int i = 0; i < kWarps; ++i) a += f[i] * accs[i * Dv + c];
-    st(out, t * so + static_cast<long>(h) * Dv + c, out_scale * (a / lt));
+    const float val = out_scale * (a / lt);
+    if (md.out_float != nullptr) md.out_float[t * md.out_float_stride + static_cast<long>(h) * Dv + c] = val;
+    else st(out, t * so + static_cast<long>(h) * Dv + c, val);
   }
 }
 
@@ -441,7 +443,9 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
       }
       float os = out_scale;
       if (md.gate != nullptr) os *= sigmoid_(md.gate[static_cast<long>(t + qi / hb) * md.gate_stride + h0 + qi % hb]);
-      st(out, static_cast<long>(t + qi / hb) * so + static_cast<long>(h0 + qi % hb) * Dv + c, os * (a / lt));
+      const long orow = t + qi / hb, ocol = static_cast<long>(h0 + qi % hb) * Dv + c;
+      if (md.out_float != nullptr) md.out_float[orow * md.out_float_stride + ocol] = os * (a / lt);
+      else st(out, orow * so + ocol, os * (a / lt));
     }
     t = tn;
   }

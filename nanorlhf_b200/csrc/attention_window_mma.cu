@@ -351,10 +351,19 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
       f = out_scale * fo / (l * fo + ex2(s2 - mt));
     }
     if (md.gate != nullptr) f *= sigmoid_(md.gate[static_cast<long>(row_t[hf]) * md.gate_stride + h0 + r % HB]);
+    float* dstf = md.out_float != nullptr
+                      ? md.out_float + static_cast<long>(row_t[hf]) * md.out_float_stride + static_cast<long>(h0 + r % HB) * Dv : nullptr;
 #pragma unroll
     for (int i = 0; i < 2 * NV; ++i) {
       const int c = i * 8 + 2 * tq;
-      if (c < Dv) *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(o[i][2 * hf] * f, o[i][2 * hf + 1] * f);
+      if (c < Dv) {
+        if (dstf != nullptr) {
+          dstf[c] = o[i][2 * hf] * f;
+          dstf[c + 1] = o[i][2 * hf + 1] * f;
+        } else {
+          *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(o[i][2 * hf] * f, o[i][2 * hf + 1] * f);
+        }
+      }
     }
   }
 }
@@ -560,7 +569,7 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
 // block per (token, query head): out = out_scale * sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s
 __global__ void window_attention_merge_kernel(const float* __restrict__ part, int nsplit, int Hq, int Dv, float out_scale,
                                               __nv_bfloat16* __restrict__ out, long so, const float* __restrict__ gate, long gate_stride,
-                                              const float* __restrict__ head_sink) {
+                                              const float* __restrict__ head_sink, float* __restrict__ out_float, long out_float_stride) {
   const long t = blockIdx.x;
   const int h = blockIdx.y;
   if (gate != nullptr) out_scale *= sigmoid_(gate[t * gate_stride + h]);
@@ -579,7 +588,8 @@ __global__ void window_attention_merge_kernel(const float* __restrict__ part, in
       const float m = p[x * (Dv + 2) + Dv];
       if (m != -INFINITY) a += ex2(m - M) * p[x * (Dv + 2) + c];
     }
-    out[t * so + static_cast<long>(h) * Dv + c] = __float2bfloat16_rn(out_scale * (a / L));
+    if (out_float != nullptr) out_float[t * out_float_stride + static_cast<long>(h) * Dv + c] = out_scale * (a / L);
+    else out[t * so + static_cast<long>(h) * Dv + c] = __float2bfloat16_rn(out_scale * (a / L));
   }
 }
 
@@ -626,7 +636,7 @@ cudaError_t launch_decode(const float* q, long sq, const void* k_cache, const vo
   if (e != cudaSuccess) return e;
   window_attention_merge_kernel<<<dim3(T, Hq), Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128, 0, s>>>(part, nsplit * 4, Hq, Dv, out_scale,
                                                                                           static_cast<__nv_bfloat16*>(out), so, md.gate,
-                                                                                          md.gate_stride, md.head_sink);
+                                                                                          md.gate_stride, md.head_sink, md.out_float, md.out_float_stride);
   return cudaGetLastError();
 }
 

@@ -224,6 +224,13 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   } else {
     TORCH_CHECK(kv_shared || v_cache.size(1) == Hkv, "window_attention: key and value heads differ");
   }
+  // a float result over bf16 pages (results that are combined further before they are rounded)
+  const bool float_out = out.scalar_type() == at::kFloat && k_cache.scalar_type() == at::kBFloat16;
+  if (float_out) {
+    TORCH_CHECK(!kv_shared, "window_attention: a float result over bf16 pages is not available with shared key / value rows");
+    md.out_float = out.data_ptr<float>();
+    md.out_float_stride = out.stride(0);
+  }
   // steps of single tokens on bf16 pages: cut the key walk into parts so that few sequences still fill the GPU
   int nsplit = 0;
   Tensor part;
@@ -240,7 +247,7 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   check(nrl_window_attention(f32(q, "q"), head_major ? q.stride(1) : q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), typed(k_cache, "k_cache"),
                              i32(block_table, "block_table"), static_cast<int>(block_table.size(1)), i32(tok_entry, "tok_entry"),
                              i32(pos, "pos"), static_cast<int>(window), static_cast<float>(scale), static_cast<float>(out_scale),
-                             out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, static_cast<int>(impl),
+                             out.data_ptr(), out.stride(0), float_out ? 0 : typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, static_cast<int>(impl),
                              nsplit, nsplit >= 1 ? part.data_ptr<float>() : nullptr, &md, cur_stream()),
         "window_attention");
 }

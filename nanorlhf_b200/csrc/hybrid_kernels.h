@@ -30,6 +30,8 @@ typedef struct {
   int dist_max;
   int v_div;                 // > 1: key head g reads the values of head g / v_div of a value cache with Hkv / v_div heads (several
                              // score maps over one set of values)
+  float* out_float;          // non-null: the result goes here as float ([T, Hq * Dv], row stride out_float_stride) whatever the pages'
+  long out_float_stride;     // type, and `out` is not written (results that are combined further before they are rounded)
 } NrlAttnMods;
 
 extern "C" {

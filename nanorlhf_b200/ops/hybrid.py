@@ -87,7 +87,8 @@ def window_attention(q, k_cache, v_cache, plan, window, scale, out_scale, out, i
     [heads, T, >= D], the layout a batched GEMM leaves.  ``softcap`` > 0: the scaled score becomes softcap * tanh(score / softcap);
     ``keep_first`` > 0: the first positions of a sequence stay visible behind the window; ``dist_bias`` [distances, heads]: row
     min(distance, distances - 1) is added to the score (after scale and cap); ``v_div`` > 1: that many neighbouring key heads read
-    one value head (several score maps over the same values)."""
+    one value head (several score maps over the same values).  ``out`` may be float32 over bf16 pages: the result is then not
+    rounded (for results that are combined further)."""
     native._count()
     _ext().window_attention(q, k_cache, v_cache, plan.block_table, plan.tok_entry, plan.pos, window, scale, out_scale, out,
                             WINDOW_IMPLS[impl], chunked, head_scale, head_slope, gate, head_sink, value_size > 0, value_size,

@@ -687,7 +687,7 @@ class HybridSampler:
             cg, ng = M.cols["g"]
             gate = U[:, cg:cg + ng]
         if ms.maps == 2:
-            a = torch.empty(T, 2 * ms.heads * ms.vdim, dtype=self.wdtype, device=dev)
+            a = torch.empty(T, 2 * ms.heads * ms.vdim, dtype=torch.float32, device=dev)    # the maps are subtracted before they are rounded
             hy.window_attention(q, M.k_cache, M.v_cache, plan, window, ms.scale, 1.0, a, head_sink=M.vec.get("sink"), softcap=ms.softcap,
                                 keep_first=ms.keep_first, dist_bias=M.vec.get("rel"), v_div=2)
             hy.diff_combine(a, M.lam, 1.0 - ms.diff, eps, gate, ms.out_scale, out, ms.heads, ms.kv_heads)

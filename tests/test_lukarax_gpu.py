@@ -334,7 +334,8 @@ def test_attention_terms(case, dtype):
     table = hy.distance_bias_table(rel.cuda(), terms["bias_max"]) if rel is not None else None
     impls = ["tile", "simple", "auto"] + (["mma"] if dtype == "bf16" and D % 8 == 0 and Dv % 8 == 0 else [])
     order = torch.randperm(16, generator=g).tolist()          # pages in no order
-    for impl in impls:
+    # over bf16 pages the result may also be asked for as float32 (maps that are subtracted before they are rounded)
+    for impl, od in [(i, wd) for i in impls] + ([(i, torch.float32) for i in impls] if dtype == "bf16" else []):
         kc = torch.zeros(16, Hk, 16, D, dtype=wd, device="cuda")
         vc = torch.zeros(16, Hv, 16, Dv, dtype=wd, device="cuda")
         got, lo = [], 0
@@ -343,7 +344,7 @@ def test_attention_terms(case, dtype):
             qs = q[lo:lo + cnt].reshape(cnt, Hq * D).cuda().contiguous()
             hy.rot_kv_write(qs, None, k[lo:lo + cnt].reshape(cnt, -1).cuda(), None, v[lo:lo + cnt].reshape(cnt, -1).cuda(), None, 0, 1.0, True,
                             False, None, None, 1e-6, plan, kc, vc)
-            out = torch.empty(cnt, Hq * Dv, dtype=wd, device="cuda")
+            out = torch.empty(cnt, Hq * Dv, dtype=od, device="cuda")
             hy.window_attention(qs, kc, vc, plan, window, scale, 1.0, out, impl=impl, head_sink=None if sink is None else sink.cuda(),
                                 softcap=terms.get("softcap", 0.0), keep_first=keep, dist_bias=table, v_div=v_div)
             got.append(out.double().cpu())
@@ -351,7 +352,7 @@ def test_attention_terms(case, dtype):
         got = torch.cat(got)
         tol = 2e-5 if dtype == "fp32" else 2.5e-2
         err = (got - want).abs().max().item()
-        assert err < tol * max(1.0, want.abs().max().item()), (impl, err)
+        assert err < tol * max(1.0, want.abs().max().item()), (impl, od, err)
 
 
 @pytest.mark.parametrize("layout,dims,D,scaling,norm,bias,own_v", [("interleaved", 8, 16, None, False, False, True),
